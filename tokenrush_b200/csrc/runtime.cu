@@ -1,0 +1,116 @@
+// Library-wide host state: error strings, the device status word, and the cache of TMA
+// tensor maps (one per distinct cache view) used by the decode and prefill kernels.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "tmap.h"
+
+static thread_local char g_last_cuda[256] = "";
+
+void trb_set_last_cuda_error(cudaError_t e, const char *file, int line) {
+    snprintf(g_last_cuda, sizeof(g_last_cuda), "%s (%s:%d)", cudaGetErrorString(e), file, line);
+}
+
+extern "C" int trb_version(void) { return 100; }
+
+extern "C" const char *trb_strerror(int code) {
+    switch (code) {
+        case TRB_OK: return "ok";
+        case TRB_E_ARG: return "bad argument (shape, null pointer or inconsistent sizes)";
+        case TRB_E_ALIGN: return "pointer or stride misses its alignment";
+        case TRB_E_CAPACITY: return "rows do not fit the cache, or the workspace is too small";
+        case TRB_E_CUDA: return g_last_cuda[0] ? g_last_cuda : "CUDA call failed";
+        case TRB_E_UNSUPPORTED: return "geometry outside what the kernels are built for";
+        case TRB_E_DEVICE: return "device status word is non-zero";
+        default: return "unknown error";
+    }
+}
+
+extern "C" int trb_device_status(uint32_t *status_out) {
+    if (!status_out) return TRB_E_ARG;
+    unsigned int v = 0, zero = 0;
+    TRB_CUDA_CHECK(cudaDeviceSynchronize());
+    TRB_CUDA_CHECK(cudaMemcpyFromSymbol(&v, trb::g_status, sizeof(v)));
+    if (v) TRB_CUDA_CHECK(cudaMemcpyToSymbol(trb::g_status, &zero, sizeof(zero)));
+    *status_out = v;
+    return TRB_OK;
+}
+
+// ------------------------------------------------------------------ tensor-map cache
+namespace trb {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+struct Key {
+    const void *base;
+    long long max_len;
+    int hkv, row_bytes, box_rows;
+    bool operator==(const Key &o) const {
+        return base == o.base && max_len == o.max_len && hkv == o.hkv && row_bytes == o.row_bytes && box_rows == o.box_rows;
+    }
+};
+struct KeyHash {
+    size_t operator()(const Key &k) const {
+        size_t h = reinterpret_cast<size_t>(k.base);
+        h ^= (size_t)k.max_len * 0x9E3779B97F4A7C15ull;
+        h ^= ((size_t)k.hkv << 40) ^ ((size_t)k.row_bytes << 20) ^ (size_t)k.box_rows;
+        return h;
+    }
+};
+
+static std::mutex g_mu;
+static std::unordered_map<Key, CUtensorMap, KeyHash> g_maps;
+
+// A [hkv, max_len, row_bytes] byte tensor seen as 4-D {128 B, row_bytes/128, max_len, hkv}
+// with a {128, row_bytes/128, box_rows, 1} box and the 128-byte swizzle.  Rows past max_len
+// read as zero.
+int get_row_tile_map(const void *base, long long max_len, int hkv, int row_bytes, int box_rows, CUtensorMap *out) {
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return TRB_E_ALIGN;
+    if (row_bytes % 128 != 0 || box_rows < 1 || box_rows > 256) return TRB_E_UNSUPPORTED;
+    Key key{base, max_len, hkv, row_bytes, box_rows};
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+        *out = it->second;
+        return TRB_OK;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return TRB_E_CUDA;
+    const cuuint32_t segs = row_bytes / 128;
+    cuuint64_t dims[4] = {128, segs, (cuuint64_t)max_len, (cuuint64_t)hkv};
+    cuuint64_t strides[3] = {128, (cuuint64_t)row_bytes, (cuuint64_t)row_bytes * (cuuint64_t)max_len};
+    cuuint32_t box[4] = {128, segs, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMap m;
+    CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_last_cuda, sizeof(g_last_cuda), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return TRB_E_CUDA;
+    }
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps.emplace(key, m);
+    *out = m;
+    return TRB_OK;
+}
+
+}  // namespace trb

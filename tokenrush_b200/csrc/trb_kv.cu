@@ -1,0 +1,9 @@
+// Single translation unit of libtrb_kv.so: the kernels share the device status word and a
+// few inline helpers, so they are compiled together.
+#include <cstring>
+
+#include "runtime.cu"
+#include "append.cu"
+#include "decode.cu"
+#include "p2p.cu"
+#include "prefill.cu"
