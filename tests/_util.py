@@ -26,13 +26,16 @@ def rel(a: np.ndarray, b: np.ndarray) -> float:
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
 
 
-def assert_attn_close(got: np.ndarray, want: np.ndarray, what=""):
-    """The parity bar of the attention outputs: max-abs 2e-3 and rel 1e-2 against fp32 math
-    over the same cache."""
+def assert_attn_close(got: np.ndarray, want: np.ndarray, what="", out_ulp=2.0 ** -8):
+    """The parity bar of the attention outputs against fp32 math over the same cache: rel 1e-2
+    over the tensor, and every element within 2e-3 plus one rounding step of the bf16 output
+    itself (2^-8 relative; at short contexts |o| is O(1) and that step alone exceeds 2e-3).
+    out_ulp=0 for outputs that were never rounded to bf16."""
     assert np.isfinite(got).all(), what
-    ma = float(np.abs(got.astype(np.float64) - want.astype(np.float64)).max())
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    tol = 2e-3 + out_ulp * np.abs(want.astype(np.float64))
     r = rel(got, want)
-    assert ma <= 2e-3 and r <= 1e-2, (what, ma, r)
+    assert (err <= tol).all() and r <= 1e-2, (what, float((err - tol).max()), float(err.max()), r)
 
 
 def oracle_state_from(state, slot=0) -> O.OracleState:

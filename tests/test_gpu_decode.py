@@ -81,6 +81,11 @@ def test_decode_m1_lengths(tb, L):
     assert_attn_close(f32_of(o).reshape(1, HQ, D), _oracle_step(st, qb, L), f"L={L}")
     o2 = tb.fused.attn_decode_fused(to_dev(qb).reshape(1, -1), None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0], st.v_scale[0])
     assert torch.equal(o, o2)                                  # replays are bit-identical
+    # the same result before the bf16 rounding of the output (the partial a sequence shard emits)
+    ml, acc = tb.fused.attn_decode_fused(to_dev(qb).reshape(1, -1), None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0],
+                                         st.v_scale[0], partial=True)
+    o32 = f32_of(acc) / f32_of(ml)[:, 1:2]
+    assert_attn_close(o32.reshape(1, HQ, D), _oracle_step(st, qb, L), f"fp32 L={L}", out_ulp=0.0)
 
 
 @pytest.mark.parametrize("M", [2, 3, 4, 5, 6, 7, 8])

@@ -227,10 +227,11 @@ extern "C" int trb_kv_append(const trb_cache_t *cache, const void *k_src, const 
     CacheView c;
     int rc = make_cache_view(cache, &c);
     if (rc) return rc;
-    if (!k_src || !v_src || n_rows < 0) return TRB_E_ARG;
+    if (n_rows < 0) return TRB_E_ARG;
     if ((rc = check_cursor(pos))) return rc;
     if (n_valid && (rc = check_cursor(n_valid))) return rc;
     if (n_rows == 0) return TRB_OK;
+    if (!k_src || !v_src) return TRB_E_ARG;
     if ((((uintptr_t)k_src | (uintptr_t)v_src) & 15) || (src_head_stride % 8) || (src_row_stride % 8)) return TRB_E_ALIGN;
     if (!pos->dev && c.ring == 0) {          // host position: capacity can be checked here
         const long long lo = pos->host - c.shard_lo;

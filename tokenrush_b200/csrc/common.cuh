@@ -73,10 +73,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2^22 polls (seconds), records TRB_ST_WAIT_TIMEOUT and
+// Bounded wait: gives up after 2^20 polls (about a second), records TRB_ST_WAIT_TIMEOUT and
 // returns false so that the caller can leave its loop instead of hanging the GPU.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
+    for (uint32_t it = 0; it < (1u << 20); ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (it > 64) __nanosleep(64);
     }

@@ -70,6 +70,14 @@ struct DecodeCfg {
     static constexpr int SMEM = MISC_OFF + MISC_BYTES + 1024;    // + slack to align the base
 };
 
+// Byte offset of (row, byte_in_row) inside a K or V tile in shared memory.  A tile is stored as
+// ROWB / 128 column blocks of [DEC_BN rows][128 bytes], each written by one TMA copy with the
+// 128-byte swizzle (16-byte chunk index XOR row mod 8), so the eight rows that one ldmatrix
+// phase reads fall into eight different bank groups.
+__device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t byte_in_row) {
+    return (byte_in_row >> 7) * (DEC_BN * 128u) + row * 128u + (((((byte_in_row >> 4) & 7u) ^ (row & 7u)) << 4) | (byte_in_row & 15u));
+}
+
 // dim of accumulator element (tile a, element i) held by lane (g, t); the query column is 2t + (i & 1)
 template <bool FP8>
 __device__ __forceinline__ int acc_dim(int a, int i, int g) {
@@ -137,8 +145,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             const int prow0 = (int)(p.ring > 0 ? vrow0 % p.ring : vrow0);
             if (lane == 0) {
                 mbar_arrive_expect_tx(&bar_full[s], 2 * C::TILE);
-                tma_load_4d(smem + s * 2 * C::TILE, &tm_k, &bar_full[s], 0, 0, prow0, j);
-                tma_load_4d(smem + s * 2 * C::TILE + C::TILE, &tm_v, &bar_full[s], 0, 0, prow0, j);
+#pragma unroll
+                for (int sg = 0; sg < C::SEGS; ++sg) {          // one 128-byte column of the rows per copy
+                    tma_load_4d(smem + s * 2 * C::TILE + sg * (DEC_BN * 128), &tm_k, &bar_full[s], 0, sg, prow0, j);
+                    tma_load_4d(smem + s * 2 * C::TILE + C::TILE + sg * (DEC_BN * 128), &tm_v, &bar_full[s], 0, sg, prow0, j);
+                }
             }
             if (FP8) {
                 const long long r = (long long)prow0 + lane;
@@ -248,7 +259,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
                     for (int cp = 0; cp < C::NCP; ++cp) {
                         uint32_t r[4];
-                        ldmatrix_x4(r, kt + swz128<C::SEGS>(grp * 16 + k_key, (2 * cp + k_chunk) * 16));
+                        ldmatrix_x4(r, kt + tile_off(grp * 16 + k_key, (2 * cp + k_chunk) * 16));
                         if (FP8) {
                             uint32_t a[4];
 #pragma unroll
@@ -327,7 +338,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
                     for (int cp = 0; cp < C::NCP; ++cp) {
                         uint32_t w[4];
-                        ldmatrix_x4_trans(w, vt + swz128<C::SEGS>(grp * 16 + v_key, (2 * cp + v_chunk) * 16));
+                        ldmatrix_x4_trans(w, vt + tile_off(grp * 16 + v_key, (2 * cp + v_chunk) * 16));
                         if (FP8) {
                             uint32_t a[4];
 #pragma unroll

@@ -80,8 +80,8 @@ static std::mutex g_mu;
 static std::unordered_map<Key, CUtensorMap, KeyHash> g_maps;
 
 // A [hkv, max_len, row_bytes] byte tensor seen as 4-D {128 B, row_bytes/128, max_len, hkv}
-// with a {128, row_bytes/128, box_rows, 1} box and the 128-byte swizzle.  Rows past max_len
-// read as zero.
+// with a {128, 1, box_rows, 1} box (one 128-byte column of box_rows rows) and the 128-byte
+// swizzle.  Rows past max_len read as zero.
 int get_row_tile_map(const void *base, long long max_len, int hkv, int row_bytes, int box_rows, CUtensorMap *out) {
     if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return TRB_E_ALIGN;
     if (row_bytes % 128 != 0 || box_rows < 1 || box_rows > 256) return TRB_E_UNSUPPORTED;
@@ -97,7 +97,7 @@ int get_row_tile_map(const void *base, long long max_len, int hkv, int row_bytes
     const cuuint32_t segs = row_bytes / 128;
     cuuint64_t dims[4] = {128, segs, (cuuint64_t)max_len, (cuuint64_t)hkv};
     cuuint64_t strides[3] = {128, (cuuint64_t)row_bytes, (cuuint64_t)row_bytes * (cuuint64_t)max_len};
-    cuuint32_t box[4] = {128, segs, (cuuint32_t)box_rows, 1};
+    cuuint32_t box[4] = {128, 1, (cuuint32_t)box_rows, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUtensorMap m;
     CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(base), dims, strides, box, estr,
