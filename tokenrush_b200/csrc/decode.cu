@@ -1,16 +1,20 @@
 // Split-K flash-decoding over the live length of an FP8 (e4m3 + per-row scale) or bf16 KV
 // cache, with the split partial-combine fused into the tail of the same launch.
 //
-// Shape of the kernel (one CTA per (split, kv head), 2 CTAs per SM):
+// Shape of the kernel (one CTA per (split, kv head), one CTA per SM):
 //   * one producer warp streams 32-key tiles of K and V into a ring of shared-memory stages
 //     with TMA (cp.async.bulk.tensor, 128-byte swizzle) and the two scale vectors with
 //     cp.async; completion is tracked by one mbarrier per stage;
-//   * six consumer warps each own an 8-row slice of the (query row x query head) rows of
-//     this kv head and a subset of the 16-key groups.  Per group: S^T = K Q^T and
-//     O^T += V^T P^T on mma.sync m16n8k16 with the KEYS (resp. dims) as the 16-row operand,
-//     so the 6..48 query rows fill n = 8 columns instead of padding a 16-row tile;
-//     e4m3 codes go to f16 in registers (exact) and the per-key scales are applied to the
-//     fp32 scores / folded into the probabilities, never to the codes;
+//   * twelve consumer warps.  The (query row x query head) rows of this kv head are cut into
+//     slices of 8; a warp owns one slice and every KW-th tile.  Per tile: S^T = K Q^T and
+//     O^T += V^T P^T on mma.sync with the KEYS (resp. head dims) as the 16-row operand, so
+//     the 6..48 query rows fill n = 8 columns instead of padding a 16-row tile;
+//   * FP8 caches: the e4m3 codes go from shared memory into m16n8k32 e4m3 MMAs as they
+//     are, with no conversion.  The bf16 query row is split into two e4m3 terms
+//     (q * 2^k = hi + lo, exact to 2^-18 of the row maximum) and so are the probabilities
+//     (8 significant bits, what a bf16 P has); the per-key scales are applied to the fp32
+//     scores, and the V scale is moved into the exponent of the probability;
+//   * bf16 caches: bf16 MMAs (m16n8k16), operands straight from ldmatrix;
 //   * online softmax in registers with warp shuffles; every warp keeps its own running
 //     (max, sum, acc) and the warps of a CTA, the CTAs of a kv head and (for sequence
 //     shards) the GPUs are all merged with the same log-sum-exp formula in a fixed order;
@@ -24,15 +28,17 @@
 
 namespace trb {
 
-constexpr int DEC_BN = 32;                       // keys per pipeline stage
-constexpr int DEC_CONSUMERS = 6;                 // consumer warps per CTA
+constexpr int DEC_BN = 32;                       // keys per pipeline stage = one unit of work
+constexpr int DEC_CONSUMERS = 12;                // consumer warps per CTA
 constexpr int DEC_CTHREADS = DEC_CONSUMERS * 32;
 constexpr int DEC_THREADS = DEC_CTHREADS + 32;   // + one producer warp
 constexpr int DEC_MAX_ROWS = 48;                 // (hq / hkv) * m
+constexpr int DEC_MAX_NT = DEC_MAX_ROWS / 8;
 constexpr int DEC_MIN_TILES = 4;                 // a split is not made smaller than this
-constexpr int DEC_STAGE_BYTES_TOTAL = 96 * 1024;
+constexpr int DEC_STAGE_BYTES_TOTAL = 192 * 1024;
 constexpr int DEC_MAX_SPLITS = 148;              // bounds the tail's weight table in shared memory
 constexpr int DEC_EPI_PAD = 4;                   // floats of padding per staged output row
+constexpr float DEC_P_SCALE = 256.f;             // probabilities are quantised as p * 256 (e4m3 hi + lo)
 
 struct DecodeParams {
     const __nv_bfloat16 *q;
@@ -41,7 +47,7 @@ struct DecodeParams {
     long long gate_rs, gate_hs;
     const float *ks, *vs;
     int m, hq, hkv, g, rows;      // rows = g * m
-    int nt, kw;                   // 8-row slices, key groups in flight (nt * kw <= 6)
+    int nt, kw;                   // 8-row slices, tiles in flight per slice (nt * kw <= 12)
     int nsplit, rows_pad;
     float scale_log2;             // softmax scale * log2(e)
     int new_rows, window, n_extra;
@@ -60,14 +66,20 @@ struct DecodeCfg {
     static constexpr int SEGS = ROWB / 128;
     static constexpr int TILE = DEC_BN * ROWB;
     static constexpr int NSTAGE_RAW = DEC_STAGE_BYTES_TOTAL / (2 * TILE);
-    static constexpr int NSTAGE = NSTAGE_RAW > 8 ? 8 : NSTAGE_RAW;
+    static constexpr int NSTAGE = NSTAGE_RAW > 16 ? 16 : NSTAGE_RAW;
     static constexpr int NCP = ROWB / 32;                        // 32-byte chunk pairs per row
     static constexpr int ACC = FP8 ? NCP * 2 : NCP;              // m16n8 accumulator tiles
+    static constexpr int QF_WORDS = FP8 ? 4 : 2;                 // query-fragment words per (slice, cp, lane)
     static constexpr int SCALE_OFF = NSTAGE * 2 * TILE;          // [NSTAGE][2][BN] floats
     static constexpr int BAR_OFF = SCALE_OFF + NSTAGE * 2 * DEC_BN * 4;
-    static constexpr int MISC_OFF = BAR_OFF + 2 * NSTAGE * 8;    // small epilogue scratch
-    static constexpr int MISC_BYTES = DEC_CONSUMERS * 8 * 2 * 4 + 64;
-    static constexpr int SMEM = MISC_OFF + MISC_BYTES + 1024;    // + slack to align the base
+    static constexpr int QF_OFF = BAR_OFF + 2 * NSTAGE * 8;      // [DEC_MAX_NT][NCP][32][QF_WORDS] words
+    static constexpr int QF_BYTES = DEC_MAX_NT * NCP * 32 * QF_WORDS * 4;
+    static constexpr int MISC_OFF = QF_OFF + QF_BYTES;
+    static constexpr int ML_BYTES = DEC_CONSUMERS * 8 * 2 * 4;   // per-warp (max, sum) of 8 columns
+    static constexpr int QINV_OFF = MISC_OFF + ML_BYTES;         // [DEC_MAX_NT][8] floats
+    static constexpr int FLAG_OFF = QINV_OFF + DEC_MAX_NT * 8 * 4;
+    static constexpr int SMEM = FLAG_OFF + 64 + 1024;            // + slack to align the base
+    static_assert(SMEM <= 227 * 1024, "shared memory budget");
 };
 
 // Byte offset of (row, byte_in_row) inside a K or V tile in shared memory.  A tile is stored as
@@ -85,8 +97,27 @@ __device__ __forceinline__ int acc_dim(int a, int i, int g) {
     return 16 * a + 8 * (i >> 1) + g;
 }
 
+// D = A(16x32 e4m3, row) * B(32x8 e4m3, col) + C, fp32 accumulate (full precision on sm_100).
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// x (fp32) -> two e4m3 codes with x ~= hi + lo; four values -> one word of hi codes, one of lo codes
+__device__ __forceinline__ void split_e4m3x4(const float (&x)[4], uint32_t &hi, uint32_t &lo) {
+    const __nv_fp8x2_storage_t h01 = __nv_cvt_float2_to_fp8x2(make_float2(x[0], x[1]), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t h23 = __nv_cvt_float2_to_fp8x2(make_float2(x[2], x[3]), __NV_SATFINITE, __NV_E4M3);
+    const float2 f01 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(h01, __NV_E4M3)));
+    const float2 f23 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(h23, __NV_E4M3)));
+    const __nv_fp8x2_storage_t l01 = __nv_cvt_float2_to_fp8x2(make_float2(x[0] - f01.x, x[1] - f01.y), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t l23 = __nv_cvt_float2_to_fp8x2(make_float2(x[2] - f23.x, x[3] - f23.y), __NV_SATFINITE, __NV_E4M3);
+    hi = (uint32_t)h01 | ((uint32_t)h23 << 16);
+    lo = (uint32_t)l01 | ((uint32_t)l23 << 16);
+}
+
 template <int D, bool FP8>
-__global__ void __maxnreg__(144)
+__global__ void __maxnreg__(128)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
     using C = DecodeCfg<D, FP8>;
     extern __shared__ uint8_t smem_raw[];
@@ -94,8 +125,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     float *sm_scale = reinterpret_cast<float *>(smem + C::SCALE_OFF);
     uint64_t *bar_full = reinterpret_cast<uint64_t *>(smem + C::BAR_OFF);
     uint64_t *bar_empty = bar_full + C::NSTAGE;
-    float *sm_ml = reinterpret_cast<float *>(smem + C::MISC_OFF);                 // [6][8][2]
-    int *sm_flag = reinterpret_cast<int *>(smem + C::MISC_OFF + DEC_CONSUMERS * 64);
+    uint32_t *sm_qf = reinterpret_cast<uint32_t *>(smem + C::QF_OFF);
+    float *sm_ml = reinterpret_cast<float *>(smem + C::MISC_OFF);                 // [12][8][2]
+    float *sm_qinv = reinterpret_cast<float *>(smem + C::QINV_OFF);               // [6][8]
+    int *sm_flag = reinterpret_cast<int *>(smem + C::FLAG_OFF);
 
     const int split = blockIdx.x, j = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -128,7 +161,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::NSTAGE; ++s) {
             mbar_init(&bar_full[s], FP8 ? 33u : 1u);
-            mbar_init(&bar_empty[s], (uint32_t)((DEC_BN / 16) * p.nt));
+            mbar_init(&bar_empty[s], (uint32_t)p.nt);
         }
         mbar_fence_init();
         tma_prefetch_desc(&tm_k);
@@ -165,42 +198,72 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
     // =============================== consumer warps ======================================
     const int g = lane >> 2, t = lane & 3;
+
+    // ---- query fragments (the B operand of S^T = K Q^T) into shared memory, once per CTA:
+    // warp w < nt prepares slice w; lane (g, t) owns column n = g (row 8w + g) and the dims
+    // that its k-slots cover.
+    if (warp < p.nt) {
+        const int r = 8 * warp + g;
+        const bool valid = r < p.rows;
+        const int qi = valid ? r / p.g : 0, hq = valid ? j * p.g + r % p.g : 0;
+        const __nv_bfloat16 *qp = p.q + ((long long)qi * p.hq + hq) * D;
+        if (FP8) {
+            float x[C::NCP][2][4];
+            float amax = 0.f;
+#pragma unroll
+            for (int cp = 0; cp < C::NCP; ++cp)
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    uint2 raw = make_uint2(0u, 0u);
+                    if (valid) raw = *reinterpret_cast<const uint2 *>(qp + 32 * cp + 16 * w + 4 * t);
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+                    x[cp][w][0] = a.x; x[cp][w][1] = a.y; x[cp][w][2] = b.x; x[cp][w][3] = b.y;
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))));
+                }
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            // power-of-two scale that puts the row maximum in [128, 256): q * sc is exact
+            int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;
+            if (amax == 0.f || e < -90) e = 7;                        // zero / tiny rows: no scaling
+            if (e > 90) e = 90;
+            const float sc = __uint_as_float((uint32_t)(127 + 7 - e) << 23);
+            if (t == 0) sm_qinv[warp * 8 + g] = __uint_as_float((uint32_t)(127 - 7 + e) << 23);
+#pragma unroll
+            for (int cp = 0; cp < C::NCP; ++cp) {
+                uint32_t h[2], l[2];
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    float y[4];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) y[b] = x[cp][w][b] * sc;
+                    split_e4m3x4(y, h[w], l[w]);
+                }
+                *reinterpret_cast<uint4 *>(&sm_qf[((warp * C::NCP + cp) * 32 + lane) * 4]) = make_uint4(h[0], h[1], l[0], l[1]);
+            }
+        } else {
+#pragma unroll
+            for (int cp = 0; cp < C::NCP; ++cp) {
+                uint32_t w0 = 0u, w1 = 0u;
+                if (valid) {
+                    w0 = *reinterpret_cast<const uint32_t *>(qp + 16 * cp + 2 * t);
+                    w1 = *reinterpret_cast<const uint32_t *>(qp + 16 * cp + 8 + 2 * t);
+                }
+                *reinterpret_cast<uint2 *>(&sm_qf[((warp * C::NCP + cp) * 32 + lane) * 2]) = make_uint2(w0, w1);
+            }
+            if (t == 0) sm_qinv[warp * 8 + g] = 1.f;
+        }
+    }
+    named_barrier(1, DEC_CTHREADS);
+
     const bool warp_on = warp < p.nt * p.kw;
     const int nt_idx = warp_on ? warp % p.nt : 0;
     const int kw_idx = warp_on ? warp / p.nt : 0;
-
-    // Query fragments (the B operand of S^T = K Q^T), column n = g of this warp's 8-row slice.
-    uint32_t qf[C::NCP][FP8 ? 2 : 1][2];
-    {
-        const int r = 8 * nt_idx + g;
-        const bool valid = warp_on && r < p.rows;
-        const int qi = valid ? r / p.g : 0, hq = valid ? j * p.g + r % p.g : 0;
-        const __nv_bfloat16 *qp = p.q + ((long long)qi * p.hq + hq) * D;
-#pragma unroll
-        for (int cp = 0; cp < C::NCP; ++cp) {
-            if (FP8) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                    for (int w = 0; w < 2; ++w) {
-                        const int d0 = 32 * cp + 16 * w + 4 * t + 2 * h;
-                        float2 f = make_float2(0.f, 0.f);
-                        if (valid) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(qp + d0));
-                        qf[cp][h][w] = pack_f16x2(f.x, f.y);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int w = 0; w < 2; ++w) {
-                    const int d0 = 16 * cp + 8 * w + 2 * t;
-                    qf[cp][0][w] = valid ? *reinterpret_cast<const uint32_t *>(qp + d0) : 0u;
-                }
-            }
-        }
-    }
+    const uint32_t *qf = sm_qf + (size_t)nt_idx * C::NCP * 32 * C::QF_WORDS + lane * C::QF_WORDS;
 
     // Visibility window of this lane's two query columns, in virtual rows of this cache.
     long long lim_hi[2], lim_lo[2];
+    float qfac[2];
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
         const int r = 8 * nt_idx + 2 * t + c;
@@ -209,8 +272,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (p.new_rows && pos + qi - p.shard_lo < hi) hi = pos + qi - p.shard_lo;
         lim_hi[c] = hi;
         lim_lo[c] = p.window > 0 ? pos + qi - p.window + 1 - p.shard_lo : 0;
+        qfac[c] = sm_qinv[nt_idx * 8 + 2 * t + c] * p.scale_log2;
     }
-    // bounds within which a whole 16-key group needs no masking for any column of the slice
+    // bounds within which a whole tile needs no masking for any column of the slice
     long long all_hi = lloc - 1, all_lo = 0;
     if (p.new_rows) {
         const long long h0 = pos + (8 * nt_idx < p.rows ? (8 * nt_idx) / p.g : 0) - p.shard_lo;
@@ -230,133 +294,160 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         for (int i = 0; i < 4; ++i) acc[a][i] = 0.f;
 
     const int mi = lane >> 3, rr = lane & 7;
-    const int k_key = rr + 8 * (mi & 1), k_chunk = mi >> 1;    // ldmatrix lane roles for K
-    const int v_key = rr + 8 * (mi >> 1), v_chunk = mi & 1;    // ... and for V (transposed)
-    bool dead = false;
+    // ldmatrix lane roles.  K (plain): matrices (keys 0-7 | 8-15) x (chunk c | c+1).
+    const uint32_t k_row = rr + 8 * (mi & 1), k_chunk = mi >> 1;
+    // V, fp8 (transposed): the four matrices are keys 0-7, 8-15, 16-23, 24-31 of one chunk.
+    // V, bf16 (transposed): (keys 0-7 | 8-15) x (chunk c | c+1) as a0..a3 of one m16n8k16.
+    const uint32_t v_row = FP8 ? (uint32_t)lane : rr + 8 * (mi >> 1), v_chunk = FP8 ? 0u : (uint32_t)(mi & 1);
 
     if (warp_on) {
-        for (int i = 0; i < my_tiles && !dead; ++i) {
-            const int s = i % C::NSTAGE;
-            bool waited = false;
 #pragma unroll 1
-            for (int grp = 0; grp < DEC_BN / 16; ++grp) {
-                const int gi = i * (DEC_BN / 16) + grp;
-                if (gi % p.kw != kw_idx) continue;
-                if (!waited) {
-                    if (!mbar_wait(&bar_full[s], (i / C::NSTAGE) & 1)) { dead = true; break; }
-                    waited = true;
-                }
-                const long long key0 = (long long)(t0 + i) * DEC_BN + grp * 16;       // virtual row of the group
-                if (key0 < lloc && key0 + 15 >= row_lo) {
-                    const uint32_t kt = smem_u32(smem + s * 2 * C::TILE);
-                    const uint32_t vt = kt + C::TILE;
-                    // ---- S^T[16 keys, 8 columns] = K Q^T, four independent accumulation chains
-                    float s4[4][4];
+        for (int i = kw_idx; i < my_tiles; i += p.kw) {
+            const int s = i % C::NSTAGE;
+            if (!mbar_wait(&bar_full[s], (i / C::NSTAGE) & 1)) break;
+            const long long key0 = (long long)(t0 + i) * DEC_BN;                    // virtual row of the tile
+            if (key0 < lloc && key0 + DEC_BN - 1 >= row_lo) {
+                const uint32_t kt = smem_u32(smem + s * 2 * C::TILE);
+                const uint32_t vt = kt + C::TILE;
+                // ---- S^T[32 keys, 8 columns] = K Q^T: two 16-key groups, two chains each
+                float sc4[2][2][4];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
+                for (int a = 0; a < 2; ++a)
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) s4[c][e] = 0.f;
+                    for (int b = 0; b < 2; ++b)
 #pragma unroll
-                    for (int cp = 0; cp < C::NCP; ++cp) {
-                        uint32_t r[4];
-                        ldmatrix_x4(r, kt + tile_off(grp * 16 + k_key, (2 * cp + k_chunk) * 16));
-                        if (FP8) {
-                            uint32_t a[4];
+                        for (int e = 0; e < 4; ++e) sc4[a][b][e] = 0.f;
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) a[e] = e4m3x2_to_f16x2((uint16_t)(r[e] & 0xffffu));
-                            mma_f16(s4[(2 * cp) & 3], a, qf[cp][0][0], qf[cp][0][1]);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) a[e] = e4m3x2_to_f16x2((uint16_t)(r[e] >> 16));
-                            mma_f16(s4[(2 * cp + 1) & 3], a, qf[cp][1][0], qf[cp][1][1]);
-                        } else {
-                            mma_bf16(s4[cp & 3], r, qf[cp][0][0], qf[cp][0][1]);
-                        }
+                for (int cp = 0; cp < C::NCP; ++cp) {
+                    uint32_t r0[4], r1[4];
+                    ldmatrix_x4(r0, kt + tile_off(k_row, (2 * cp + k_chunk) * 16));
+                    ldmatrix_x4(r1, kt + tile_off(16 + k_row, (2 * cp + k_chunk) * 16));
+                    if (FP8) {
+                        const uint4 qv = *reinterpret_cast<const uint4 *>(qf + cp * 32 * 4);
+                        mma_e4m3(sc4[0][0], r0, qv.x, qv.y);
+                        mma_e4m3(sc4[0][1], r0, qv.z, qv.w);
+                        mma_e4m3(sc4[1][0], r1, qv.x, qv.y);
+                        mma_e4m3(sc4[1][1], r1, qv.z, qv.w);
+                    } else {
+                        const uint2 qv = *reinterpret_cast<const uint2 *>(qf + cp * 32 * 2);
+                        mma_bf16(sc4[0][cp & 1], r0, qv.x, qv.y);
+                        mma_bf16(sc4[1][cp & 1], r1, qv.x, qv.y);
                     }
-                    float tv[4];
+                }
+                // tv[grp][e], e = 2*h + c -> key 16*grp + g + 8h, column 2t + c
+                float tv[2][4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) tv[e] = (s4[0][e] + s4[1][e]) + (s4[2][e] + s4[3][e]);
+                for (int a = 0; a < 2; ++a)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) tv[a][e] = sc4[a][0][e] + sc4[a][1][e];
 
-                    // ---- per-key factors: score scale, and the V scale moved into the exponent
-                    float ka[2], vb[2], vr[2];
+                // ---- per-key factors: score scale, and the V scale moved into the exponent
+                float vr[2][2];
+#pragma unroll
+                for (int a = 0; a < 2; ++a)
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         if (FP8) {
-                            const float ksc = sm_scale[(s * 2 + 0) * DEC_BN + grp * 16 + g + 8 * h];
-                            const float vsc = sm_scale[(s * 2 + 1) * DEC_BN + grp * 16 + g + 8 * h];
-                            ka[h] = ksc * p.scale_log2;
-                            vb[h] = __log2f(vsc);
-                            vr[h] = __frcp_rn(vsc);
+                            const float ksc = sm_scale[(s * 2 + 0) * DEC_BN + a * 16 + g + 8 * h];
+                            const float vsc = sm_scale[(s * 2 + 1) * DEC_BN + a * 16 + g + 8 * h];
+                            const float vb = __log2f(vsc);
+                            vr[a][h] = __frcp_rn(vsc);
+                            tv[a][2 * h + 0] = fmaf(tv[a][2 * h + 0], ksc * qfac[0], vb);
+                            tv[a][2 * h + 1] = fmaf(tv[a][2 * h + 1], ksc * qfac[1], vb);
                         } else {
-                            ka[h] = p.scale_log2; vb[h] = 0.f; vr[h] = 1.f;
+                            vr[a][h] = 1.f;
+                            tv[a][2 * h + 0] *= qfac[0];
+                            tv[a][2 * h + 1] *= qfac[1];
                         }
                     }
-                    // tv[e]: e = 2*h + c  ->  key g + 8h, column 2t + c
+                const bool full_vis = key0 + DEC_BN - 1 <= all_hi && key0 >= all_lo;
+                if (!full_vis) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) tv[e] = fmaf(tv[e], ka[e >> 1], vb[e >> 1]);
-                    const bool full_vis = key0 + 15 <= all_hi && key0 >= all_lo;
-                    if (!full_vis) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const long long kv = key0 + g + 8 * (e >> 1);
-                            const bool vis = kv <= lim_hi[e & 1] && kv >= lim_lo[e & 1];
-                            if (!vis) { tv[e] = -INFINITY; }
-                        }
+                    for (int a = 0; a < 2; ++a)
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const long long kv = key0 + g + 8 * h;
-                            if (kv >= lloc) vr[h] = 0.f;                       // never-written rows: scale may be anything
+                            const long long kv = key0 + a * 16 + g + 8 * h;
+                            if (!(kv <= lim_hi[0] && kv >= lim_lo[0])) tv[a][2 * h + 0] = -INFINITY;
+                            if (!(kv <= lim_hi[1] && kv >= lim_lo[1])) tv[a][2 * h + 1] = -INFINITY;
+                            if (kv >= lloc) vr[a][h] = 0.f;                  // never-written rows: scale may be anything
                         }
-                    }
-                    // ---- online softmax over the keys (rows of S^T): reduce across the g lanes
-                    float pr[4], alpha[2];
+                }
+                // ---- online softmax over the 32 keys (rows of S^T): reduce across the g lanes
+                float alpha[2];
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        float ml = fmaxf(tv[c], tv[2 + c]);
-                        ml = fmaxf(ml, __shfl_xor_sync(0xffffffffu, ml, 4));
-                        ml = fmaxf(ml, __shfl_xor_sync(0xffffffffu, ml, 8));
-                        ml = fmaxf(ml, __shfl_xor_sync(0xffffffffu, ml, 16));
-                        const float mn = fmaxf(mx[c], ml);
-                        const float msafe = mn == -INFINITY ? 0.f : mn;
-                        alpha[c] = fast_exp2(mx[c] - msafe);
-                        pr[c] = fast_exp2(tv[c] - msafe);
-                        pr[2 + c] = fast_exp2(tv[2 + c] - msafe);
-                        ls[c] = fmaf(ls[c], alpha[c], fmaf(pr[c], vr[0], pr[2 + c] * vr[1]));
-                        mx[c] = mn;
-                    }
-                    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+                for (int c = 0; c < 2; ++c) {
+                    float ml = fmaxf(fmaxf(tv[0][c], tv[0][2 + c]), fmaxf(tv[1][c], tv[1][2 + c]));
+                    ml = fmaxf(ml, __shfl_xor_sync(0xffffffffu, ml, 4));
+                    ml = fmaxf(ml, __shfl_xor_sync(0xffffffffu, ml, 8));
+                    ml = fmaxf(ml, __shfl_xor_sync(0xffffffffu, ml, 16));
+                    const float mn = fmaxf(mx[c], ml);
+                    const float msafe = mn == -INFINITY ? 0.f : mn;
+                    alpha[c] = fast_exp2(mx[c] - msafe);
+                    float lsum = 0.f;
 #pragma unroll
-                        for (int a = 0; a < C::ACC; ++a) {
-                            acc[a][0] *= alpha[0]; acc[a][1] *= alpha[1];
-                            acc[a][2] *= alpha[0]; acc[a][3] *= alpha[1];
+                    for (int a = 0; a < 2; ++a)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const float pv = fast_exp2(tv[a][2 * h + c] - msafe);
+                            tv[a][2 * h + c] = pv;
+                            lsum = fmaf(pv, vr[a][h], lsum);
                         }
+                    ls[c] = fmaf(ls[c], alpha[c], lsum);
+                    mx[c] = mn;
+                }
+                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+                    for (int a = 0; a < C::ACC; ++a) {
+                        acc[a][0] *= alpha[0]; acc[a][1] *= alpha[1];
+                        acc[a][2] *= alpha[0]; acc[a][3] *= alpha[1];
                     }
-                    // ---- P^T as the B operand: transpose the 8x8 blocks across the warp
-                    const uint32_t w0 = FP8 ? pack_f16x2(pr[0], pr[1]) : pack_bf16x2(pr[0], pr[1]);
-                    const uint32_t w1 = FP8 ? pack_f16x2(pr[2], pr[3]) : pack_bf16x2(pr[2], pr[3]);
-                    const uint32_t pb0 = movmatrix_trans(w0), pb1 = movmatrix_trans(w1);
+                }
+                if (FP8) {
+                    // ---- P^T as the B operand of m16n8k32: per 16-key group pack the codes of keys
+                    // (g, g+8) of one column into 16 bits, transpose the 8x8 blocks of such units
+                    // across the warp; k-slots 4t..4t+3 then hold keys 2t, 2t+8, 2t+1, 2t+9.
+                    uint32_t ph[2], pl[2];
+#pragma unroll
+                    for (int a = 0; a < 2; ++a) {
+                        const float y[4] = {tv[a][0] * DEC_P_SCALE, tv[a][2] * DEC_P_SCALE,      // column 2t:   keys g, g+8
+                                            tv[a][1] * DEC_P_SCALE, tv[a][3] * DEC_P_SCALE};     // column 2t+1: keys g, g+8
+                        uint32_t hi, lo;
+                        split_e4m3x4(y, hi, lo);
+                        ph[a] = movmatrix_trans(hi);
+                        pl[a] = movmatrix_trans(lo);
+                    }
                     // ---- O^T[D dims, 8 columns] += V^T P^T
 #pragma unroll
                     for (int cp = 0; cp < C::NCP; ++cp) {
-                        uint32_t w[4];
-                        ldmatrix_x4_trans(w, vt + tile_off(grp * 16 + v_key, (2 * cp + v_chunk) * 16));
-                        if (FP8) {
-                            uint32_t a[4];
+                        uint32_t w[4], x[4];
+                        ldmatrix_x4_trans(w, vt + tile_off(v_row, (2 * cp) * 16));
+                        ldmatrix_x4_trans(x, vt + tile_off(v_row, (2 * cp + 1) * 16));
+                        uint32_t av[4];
+                        av[0] = prmt(w[0], w[1], 0x6240u); av[1] = prmt(x[0], x[1], 0x6240u);
+                        av[2] = prmt(w[2], w[3], 0x6240u); av[3] = prmt(x[2], x[3], 0x6240u);
+                        mma_e4m3(acc[2 * cp], av, ph[0], ph[1]);
+                        mma_e4m3(acc[2 * cp], av, pl[0], pl[1]);
+                        av[0] = prmt(w[0], w[1], 0x7351u); av[1] = prmt(x[0], x[1], 0x7351u);
+                        av[2] = prmt(w[2], w[3], 0x7351u); av[3] = prmt(x[2], x[3], 0x7351u);
+                        mma_e4m3(acc[2 * cp + 1], av, ph[0], ph[1]);
+                        mma_e4m3(acc[2 * cp + 1], av, pl[0], pl[1]);
+                    }
+                } else {
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) w[e] = prmt(w[e], 0u, 0x3120u);
+                    for (int a = 0; a < 2; ++a) {
+                        const uint32_t pb0 = movmatrix_trans(pack_bf16x2(tv[a][0], tv[a][1]));
+                        const uint32_t pb1 = movmatrix_trans(pack_bf16x2(tv[a][2], tv[a][3]));
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) a[e] = e4m3x2_to_f16x2((uint16_t)(w[e] & 0xffffu));
-                            mma_f16(acc[2 * cp], a, pb0, pb1);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) a[e] = e4m3x2_to_f16x2((uint16_t)(w[e] >> 16));
-                            mma_f16(acc[2 * cp + 1], a, pb0, pb1);
-                        } else {
+                        for (int cp = 0; cp < C::NCP; ++cp) {
+                            uint32_t w[4];
+                            ldmatrix_x4_trans(w, vt + tile_off(a * 16 + v_row, (2 * cp + v_chunk) * 16));
                             mma_bf16(acc[cp], w, pb0, pb1);
                         }
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_empty[s]);
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_empty[s]);
         }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -382,7 +473,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         for (int c = 0; c < 2; ++c) {
             float mg = -INFINITY;
             for (int k = 0; k < p.kw; ++k) mg = fmaxf(mg, sm_ml[((k * p.nt + nt_idx) * 8 + 2 * t + c) * 2]);
-            wgt[c] = mg == -INFINITY ? 0.f : fast_exp2(mx[c] - mg);
+            wgt[c] = mg == -INFINITY ? 0.f : fast_exp2(mx[c] - mg) * (FP8 ? 1.f / DEC_P_SCALE : 1.f);
         }
 #pragma unroll
         for (int a = 0; a < C::ACC; ++a)
@@ -391,7 +482,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 stage_acc[(warp * 8 + 2 * t + (i & 1)) * SROW + acc_dim<FP8>(a, i, g)] = acc[a][i] * wgt[i & 1];
     }
     named_barrier(1, DEC_CTHREADS);
-    const int tid = threadIdx.x;                                       // 0..191 here
+    const int tid = threadIdx.x;                                       // 0..383 here
     const long long part_base = ((long long)j * p.nsplit + split) * p.rows_pad;
     for (int item = tid; item < p.nt * 8 * (D / 4); item += DEC_CTHREADS) {
         const int row = item / (D / 4), d4 = (item % (D / 4)) * 4;
@@ -471,9 +562,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         const long long grow = (long long)qi * p.hq + hq;
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
         const float *wr = sm_w + row * n_parts;
-#pragma unroll 4
+        const float *pa = p.part_acc + ((long long)j * p.nsplit * p.rows_pad + row) * D + d4;
+        const long long pstride = (long long)p.rows_pad * D;
+#pragma unroll 8
         for (int s = 0; s < active; ++s) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(&p.part_acc[(((long long)j * p.nsplit + s) * p.rows_pad + row) * D + d4]));
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(pa + s * pstride));
             const float w = wr[s];
             o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
         }
@@ -589,9 +682,9 @@ static int sm_count() {
     return g_sm_count;
 }
 
-// splits per kv head: two CTAs per SM over all heads
+// splits per kv head: one CTA per SM over all heads
 static int decode_nsplit(int hkv) {
-    int n = (2 * sm_count()) / hkv;
+    int n = sm_count() / hkv;
     if (n > DEC_MAX_SPLITS) n = DEC_MAX_SPLITS;
     return n < 1 ? 1 : n;
 }
