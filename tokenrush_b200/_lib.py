@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libtrb_kv.so")
+LIB_PATH = os.environ.get("TRB_KV_LIB") or os.path.join(HERE, "libtrb_kv.so")
 
 TRB_KV_BF16, TRB_KV_FP8 = 0, 1
 ST_CURSOR_RANGE, ST_WAIT_TIMEOUT, ST_PEER_TIMEOUT = 1, 2, 4

@@ -2,18 +2,20 @@
 // cache, with the split partial-combine fused into the tail of the same launch.
 //
 // Shape of the kernel (one CTA per (split, kv head), one CTA per SM):
-//   * one producer warp streams 32-key tiles of K and V into a ring of shared-memory stages
-//     with TMA (cp.async.bulk.tensor, 128-byte swizzle) and the two scale vectors with
-//     cp.async; completion is tracked by one mbarrier per stage;
-//   * twelve consumer warps.  The (query row x query head) rows of this kv head are cut into
-//     slices of 8; a warp owns one slice and every KW-th tile.  Per tile: S^T = K Q^T and
+//   * 32-key tiles of K and V stream into a ring of shared-memory stages with TMA
+//     (cp.async.bulk.tensor, 128-byte swizzle), the two scale vectors with cp.async; one
+//     mbarrier per stage tracks arrival, a second one the release of the stage;
+//   * twelve warps, no dedicated producer.  The (query row x query head) rows of this kv head
+//     are cut into slices of 8; a warp owns one slice and every KW-th tile, and the slice-0
+//     warp of a tile refills its stage as soon as every slice has left it.  Per tile: S^T = K Q^T and
 //     O^T += V^T P^T on mma.sync with the KEYS (resp. head dims) as the 16-row operand, so
 //     the 6..48 query rows fill n = 8 columns instead of padding a 16-row tile;
-//   * FP8 caches: the e4m3 codes go from shared memory into m16n8k32 e4m3 MMAs as they
-//     are, with no conversion.  The bf16 query row is split into two e4m3 terms
-//     (q * 2^k = hi + lo, exact to 2^-18 of the row maximum) and so are the probabilities
-//     (8 significant bits, what a bf16 P has); the per-key scales are applied to the fp32
-//     scores, and the V scale is moved into the exponent of the probability;
+//   * FP8 caches: e4m3 codes become f16 in registers (one cvt per pair, exact) and feed f16
+//     MMAs (m16n8k16) against an f16 copy of the query and f16 probabilities; the per-key
+//     scales are applied to the fp32 scores, and the V scale is moved into the exponent of
+//     the probability, so the codes themselves are never scaled.  (mma.sync with e4m3
+//     operands is not native on sm_100: it compiles to conversions plus f16 MMAs plus
+//     separate fp32 adds, several times the instruction count of converting once.)
 //   * bf16 caches: bf16 MMAs (m16n8k16), operands straight from ldmatrix;
 //   * online softmax in registers with warp shuffles; every warp keeps its own running
 //     (max, sum, acc) and the warps of a CTA, the CTAs of a kv head and (for sequence
@@ -31,7 +33,7 @@ namespace trb {
 constexpr int DEC_BN = 32;                       // keys per pipeline stage = one unit of work
 constexpr int DEC_CONSUMERS = 12;                // consumer warps per CTA
 constexpr int DEC_CTHREADS = DEC_CONSUMERS * 32;
-constexpr int DEC_THREADS = DEC_CTHREADS + 32;   // + one producer warp
+constexpr int DEC_THREADS = DEC_CTHREADS;        // no dedicated producer: slice-0 warps issue their group's loads
 constexpr int DEC_MAX_ROWS = 48;                 // (hq / hkv) * m
 constexpr int DEC_MAX_NT = DEC_MAX_ROWS / 8;
 constexpr int DEC_MIN_TILES = 4;                 // a split is not made smaller than this
@@ -55,7 +57,7 @@ struct DecodeParams {
     Cursor pos;
     long long max_len, ring, shard_lo;
     int sharded;
-    unsigned int *counters;
+    unsigned int *counters;       // [3][64]: tickets, slice claims, launch epochs (per kv head)
     float *part_ml, *part_acc;
     float *shard_ml, *shard_acc;
 };
@@ -117,7 +119,7 @@ __device__ __forceinline__ void split_e4m3x4(const float (&x)[4], uint32_t &hi, 
 }
 
 template <int D, bool FP8>
-__global__ void __maxnreg__(128)
+__global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
     using C = DecodeCfg<D, FP8>;
     extern __shared__ uint8_t smem_raw[];
@@ -169,35 +171,42 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
     __syncthreads();
 
-    // =============================== producer warp =======================================
-    if (warp == DEC_CONSUMERS) {
-        for (int i = 0; i < my_tiles; ++i) {
-            const int s = i % C::NSTAGE;
-            if (i >= C::NSTAGE && !mbar_wait(&bar_empty[s], ((i / C::NSTAGE) & 1) ^ 1)) break;
-            const long long vrow0 = (long long)(t0 + i) * DEC_BN;
-            const int prow0 = (int)(p.ring > 0 ? vrow0 % p.ring : vrow0);
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&bar_full[s], 2 * C::TILE);
-#pragma unroll
-                for (int sg = 0; sg < C::SEGS; ++sg) {          // one 128-byte column of the rows per copy
-                    tma_load_4d(smem + s * 2 * C::TILE + sg * (DEC_BN * 128), &tm_k, &bar_full[s], 0, sg, prow0, j);
-                    tma_load_4d(smem + s * 2 * C::TILE + C::TILE + sg * (DEC_BN * 128), &tm_v, &bar_full[s], 0, sg, prow0, j);
-                }
-            }
-            if (FP8) {
-                const long long r = (long long)prow0 + lane;
-                const bool ok = r < p.max_len;
-                const long long off = (long long)j * p.max_len + (ok ? r : 0);
-                cp_async_4(&sm_scale[(s * 2 + 0) * DEC_BN + lane], p.ks + off, ok ? 4u : 0u);
-                cp_async_4(&sm_scale[(s * 2 + 1) * DEC_BN + lane], p.vs + off, ok ? 4u : 0u);
-                cp_async_mbar_arrive_noinc(&bar_full[s]);
-            }
-        }
-        return;
-    }
-
     // =============================== consumer warps ======================================
     const int g = lane >> 2, t = lane & 3;
+
+    const bool warp_on = warp < p.nt * p.kw;
+    const int nt_idx = warp_on ? warp % p.nt : 0;
+    const int kw_idx = warp_on ? warp / p.nt : 0;
+    const unsigned int epoch = threadIdx.x == 0 ? *(volatile unsigned int *)&p.counters[128 + j] : 0u;
+
+    // Loads of tile i into stage i % NSTAGE: issued by the slice-0 warp of the group that owns
+    // the stage at that moment (TMA by lane 0, one scale pair per lane with cp.async).
+    auto issue_tile = [&](int i) {
+        const int s = i % C::NSTAGE;
+        const long long vrow0 = (long long)(t0 + i) * DEC_BN;
+        const int prow0 = (int)(p.ring > 0 ? vrow0 % p.ring : vrow0);
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&bar_full[s], 2 * C::TILE);
+#pragma unroll
+            for (int sg = 0; sg < C::SEGS; ++sg) {              // one 128-byte column of the rows per copy
+                tma_load_4d(smem + s * 2 * C::TILE + sg * (DEC_BN * 128), &tm_k, &bar_full[s], 0, sg, prow0, j);
+                tma_load_4d(smem + s * 2 * C::TILE + C::TILE + sg * (DEC_BN * 128), &tm_v, &bar_full[s], 0, sg, prow0, j);
+            }
+        }
+        if (FP8) {
+            const long long r = (long long)prow0 + lane;
+            const bool ok = r < p.max_len;
+            const long long off = (long long)j * p.max_len + (ok ? r : 0);
+            cp_async_4(&sm_scale[(s * 2 + 0) * DEC_BN + lane], p.ks + off, ok ? 4u : 0u);
+            cp_async_4(&sm_scale[(s * 2 + 1) * DEC_BN + lane], p.vs + off, ok ? 4u : 0u);
+            cp_async_mbar_arrive_noinc(&bar_full[s]);
+        }
+    };
+    const bool issuer = warp_on && nt_idx == 0;
+#ifndef TRB_DEC_NOLOAD
+    if (issuer)
+        for (int i = kw_idx; i < my_tiles && i < C::NSTAGE; i += p.kw) issue_tile(i);
+#endif
 
     // ---- query fragments (the B operand of S^T = K Q^T) into shared memory, once per CTA:
     // warp w < nt prepares slice w; lane (g, t) owns column n = g (row 8w + g) and the dims
@@ -208,39 +217,24 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         const int qi = valid ? r / p.g : 0, hq = valid ? j * p.g + r % p.g : 0;
         const __nv_bfloat16 *qp = p.q + ((long long)qi * p.hq + hq) * D;
         if (FP8) {
-            float x[C::NCP][2][4];
-            float amax = 0.f;
-#pragma unroll
-            for (int cp = 0; cp < C::NCP; ++cp)
+            // f16 copies of the bf16 query (exact for |q| < 65504): word [h][w] of chunk pair cp holds
+            // dims 32cp + 16w + 4t + 2h, +1, the k-slots that the low / high half-words of the
+            // ldmatrix registers of K map to
+#pragma unroll 2
+            for (int cp = 0; cp < C::NCP; ++cp) {
+                uint32_t f[2][2];
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
                     uint2 raw = make_uint2(0u, 0u);
                     if (valid) raw = *reinterpret_cast<const uint2 *>(qp + 32 * cp + 16 * w + 4 * t);
                     const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
                     const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
-                    x[cp][w][0] = a.x; x[cp][w][1] = a.y; x[cp][w][2] = b.x; x[cp][w][3] = b.y;
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))));
+                    f[0][w] = pack_f16x2(a.x, a.y);
+                    f[1][w] = pack_f16x2(b.x, b.y);
                 }
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            // power-of-two scale that puts the row maximum in [128, 256): q * sc is exact
-            int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;
-            if (amax == 0.f || e < -90) e = 7;                        // zero / tiny rows: no scaling
-            if (e > 90) e = 90;
-            const float sc = __uint_as_float((uint32_t)(127 + 7 - e) << 23);
-            if (t == 0) sm_qinv[warp * 8 + g] = __uint_as_float((uint32_t)(127 - 7 + e) << 23);
-#pragma unroll
-            for (int cp = 0; cp < C::NCP; ++cp) {
-                uint32_t h[2], l[2];
-#pragma unroll
-                for (int w = 0; w < 2; ++w) {
-                    float y[4];
-#pragma unroll
-                    for (int b = 0; b < 4; ++b) y[b] = x[cp][w][b] * sc;
-                    split_e4m3x4(y, h[w], l[w]);
-                }
-                *reinterpret_cast<uint4 *>(&sm_qf[((warp * C::NCP + cp) * 32 + lane) * 4]) = make_uint4(h[0], h[1], l[0], l[1]);
+                *reinterpret_cast<uint4 *>(&sm_qf[((warp * C::NCP + cp) * 32 + lane) * 4]) = make_uint4(f[0][0], f[0][1], f[1][0], f[1][1]);
             }
+            if (t == 0) sm_qinv[warp * 8 + g] = 1.f;
         } else {
 #pragma unroll
             for (int cp = 0; cp < C::NCP; ++cp) {
@@ -254,36 +248,27 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             if (t == 0) sm_qinv[warp * 8 + g] = 1.f;
         }
     }
-    named_barrier(1, DEC_CTHREADS);
+    __syncthreads();
 
-    const bool warp_on = warp < p.nt * p.kw;
-    const int nt_idx = warp_on ? warp % p.nt : 0;
-    const int kw_idx = warp_on ? warp / p.nt : 0;
     const uint32_t *qf = sm_qf + (size_t)nt_idx * C::NCP * 32 * C::QF_WORDS + lane * C::QF_WORDS;
 
-    // Visibility window of this lane's two query columns, in virtual rows of this cache.
-    long long lim_hi[2], lim_lo[2];
+    // Visibility window of this lane's two query columns, in virtual rows of this cache
+    // (32-bit: the host rejects caches of 2^31 rows or more).
+    const int lloc_i = (int)lloc, row_lo_i = (int)row_lo;
+    const int pos_loc = (int)(pos - p.shard_lo);               // may be negative on a later shard
     float qfac[2];
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-        const int r = 8 * nt_idx + 2 * t + c;
-        const int qi = r < p.rows ? r / p.g : 0;               // padding rows copy row 0's window
-        long long hi = lloc - 1;
-        if (p.new_rows && pos + qi - p.shard_lo < hi) hi = pos + qi - p.shard_lo;
-        lim_hi[c] = hi;
-        lim_lo[c] = p.window > 0 ? pos + qi - p.window + 1 - p.shard_lo : 0;
-        qfac[c] = sm_qinv[nt_idx * 8 + 2 * t + c] * p.scale_log2;
-    }
+    for (int c = 0; c < 2; ++c) qfac[c] = sm_qinv[nt_idx * 8 + 2 * t + c] * p.scale_log2;
     // bounds within which a whole tile needs no masking for any column of the slice
-    long long all_hi = lloc - 1, all_lo = 0;
+    int all_hi = lloc_i - 1, all_lo = 0;
     if (p.new_rows) {
-        const long long h0 = pos + (8 * nt_idx < p.rows ? (8 * nt_idx) / p.g : 0) - p.shard_lo;
+        const int h0 = pos_loc + (8 * nt_idx < p.rows ? (8 * nt_idx) / p.g : 0);
         if (h0 < all_hi) all_hi = h0;
     }
     if (p.window > 0) {
         int rmax = 8 * nt_idx + 7;
         if (rmax >= p.rows) rmax = p.rows - 1;
-        all_lo = pos + (rmax >= 0 ? rmax / p.g : 0) - p.window + 1 - p.shard_lo;
+        all_lo = pos_loc + (rmax >= 0 ? rmax / p.g : 0) - p.window + 1;
     }
 
     float mx[2] = {-INFINITY, -INFINITY}, ls[2] = {0.f, 0.f};
@@ -293,22 +278,34 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[a][i] = 0.f;
 
+    // ldmatrix lane roles; the byte offset of a lane's row inside a tile splits into a lane part
+    // (row * 128 and the swizzle XOR, which depends on chunk mod 8 only) and compile-time parts
+    // (128-byte column block, 16-key group), so one address per chunk-pair-mod-4 serves a tile.
     const int mi = lane >> 3, rr = lane & 7;
-    // ldmatrix lane roles.  K (plain): matrices (keys 0-7 | 8-15) x (chunk c | c+1).
-    const uint32_t k_row = rr + 8 * (mi & 1), k_chunk = mi >> 1;
-    // V, fp8 (transposed): the four matrices are keys 0-7, 8-15, 16-23, 24-31 of one chunk.
-    // V, bf16 (transposed): (keys 0-7 | 8-15) x (chunk c | c+1) as a0..a3 of one m16n8k16.
-    const uint32_t v_row = FP8 ? (uint32_t)lane : rr + 8 * (mi >> 1), v_chunk = FP8 ? 0u : (uint32_t)(mi & 1);
+    // K (plain): matrices (keys 0-7 | 8-15) x (chunk c | c+1)
+    const uint32_t k_lane = (uint32_t)(rr + 8 * (mi & 1)) * 128u, k_chunk = (uint32_t)(mi >> 1);
+    // V (transposed): (keys 0-7 | 8-15) x (chunk c | c+1) as a0..a3 of one m16n8k16
+    const uint32_t v_lane = (uint32_t)(rr + 8 * (mi >> 1)) * 128u, v_chunk = (uint32_t)(mi & 1);
+    const uint32_t urr = (uint32_t)rr;
+    constexpr int NSEG = C::NCP / 4 > 0 ? C::NCP / 4 : 1;      // 128-byte column blocks per row
+    constexpr int NQ = C::NCP < 4 ? C::NCP : 4;                 // chunk pairs per column block
 
     if (warp_on) {
 #pragma unroll 1
         for (int i = kw_idx; i < my_tiles; i += p.kw) {
             const int s = i % C::NSTAGE;
+#ifndef TRB_DEC_NOLOAD
             if (!mbar_wait(&bar_full[s], (i / C::NSTAGE) & 1)) break;
-            const long long key0 = (long long)(t0 + i) * DEC_BN;                    // virtual row of the tile
-            if (key0 < lloc && key0 + DEC_BN - 1 >= row_lo) {
+#endif
+            const int key0 = (t0 + i) * DEC_BN;                                    // virtual row of the tile
+#ifdef TRB_DEC_NOCOMPUTE
+            if (false) {
+#else
+            if (key0 < lloc_i && key0 + DEC_BN - 1 >= row_lo_i) {
+#endif
                 const uint32_t kt = smem_u32(smem + s * 2 * C::TILE);
                 const uint32_t vt = kt + C::TILE;
+                const float *scl = sm_scale + s * 2 * DEC_BN;
                 // ---- S^T[32 keys, 8 columns] = K Q^T: two 16-key groups, two chains each
                 float sc4[2][2][4];
 #pragma unroll
@@ -318,20 +315,35 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
                         for (int e = 0; e < 4; ++e) sc4[a][b][e] = 0.f;
 #pragma unroll
-                for (int cp = 0; cp < C::NCP; ++cp) {
-                    uint32_t r0[4], r1[4];
-                    ldmatrix_x4(r0, kt + tile_off(k_row, (2 * cp + k_chunk) * 16));
-                    ldmatrix_x4(r1, kt + tile_off(16 + k_row, (2 * cp + k_chunk) * 16));
-                    if (FP8) {
-                        const uint4 qv = *reinterpret_cast<const uint4 *>(qf + cp * 32 * 4);
-                        mma_e4m3(sc4[0][0], r0, qv.x, qv.y);
-                        mma_e4m3(sc4[0][1], r0, qv.z, qv.w);
-                        mma_e4m3(sc4[1][0], r1, qv.x, qv.y);
-                        mma_e4m3(sc4[1][1], r1, qv.z, qv.w);
-                    } else {
-                        const uint2 qv = *reinterpret_cast<const uint2 *>(qf + cp * 32 * 2);
-                        mma_bf16(sc4[0][cp & 1], r0, qv.x, qv.y);
-                        mma_bf16(sc4[1][cp & 1], r1, qv.x, qv.y);
+                for (int q = 0; q < NQ; ++q) {
+                    const uint32_t ka = kt + k_lane + (((2u * q + k_chunk) ^ urr) << 4);
+#pragma unroll
+                    for (int sg = 0; sg < NSEG; ++sg) {
+                        const int cp = 4 * sg + q;
+                        uint32_t r0[4], r1[4];
+                        ldmatrix_x4(r0, ka + sg * (DEC_BN * 128));
+                        ldmatrix_x4(r1, ka + sg * (DEC_BN * 128) + 16 * 128);
+                        if (FP8) {
+                            // e4m3 -> f16 in registers (exact); low half-words feed one MMA, high ones the next
+                            const uint4 qv = *reinterpret_cast<const uint4 *>(qf + cp * 32 * 4);
+                            uint32_t af[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r0[e] & 0xffffu));
+                            mma_f16(sc4[0][0], af, qv.x, qv.y);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r0[e] >> 16));
+                            mma_f16(sc4[0][1], af, qv.z, qv.w);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r1[e] & 0xffffu));
+                            mma_f16(sc4[1][0], af, qv.x, qv.y);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r1[e] >> 16));
+                            mma_f16(sc4[1][1], af, qv.z, qv.w);
+                        } else {
+                            const uint2 qv = *reinterpret_cast<const uint2 *>(qf + cp * 32 * 2);
+                            mma_bf16(sc4[0][sg & 1], r0, qv.x, qv.y);
+                            mma_bf16(sc4[1][sg & 1], r1, qv.x, qv.y);
+                        }
                     }
                 }
                 // tv[grp][e], e = 2*h + c -> key 16*grp + g + 8h, column 2t + c
@@ -348,10 +360,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         if (FP8) {
-                            const float ksc = sm_scale[(s * 2 + 0) * DEC_BN + a * 16 + g + 8 * h];
-                            const float vsc = sm_scale[(s * 2 + 1) * DEC_BN + a * 16 + g + 8 * h];
+                            const float ksc = scl[a * 16 + g + 8 * h];
+                            const float vsc = scl[DEC_BN + a * 16 + g + 8 * h];
                             const float vb = __log2f(vsc);
-                            vr[a][h] = __frcp_rn(vsc);
+                            vr[a][h] = __fdividef(1.f, vsc);
                             tv[a][2 * h + 0] = fmaf(tv[a][2 * h + 0], ksc * qfac[0], vb);
                             tv[a][2 * h + 1] = fmaf(tv[a][2 * h + 1], ksc * qfac[1], vb);
                         } else {
@@ -360,17 +372,25 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                             tv[a][2 * h + 1] *= qfac[1];
                         }
                     }
-                const bool full_vis = key0 + DEC_BN - 1 <= all_hi && key0 >= all_lo;
-                if (!full_vis) {
+                if (!(key0 + DEC_BN - 1 <= all_hi && key0 >= all_lo)) {
+                    // rare (the tiles at the ends of the live range): the limits of this lane's two
+                    // columns are recomputed here rather than kept in registers
 #pragma unroll
-                    for (int a = 0; a < 2; ++a)
+                    for (int c = 0; c < 2; ++c) {
+                        const int r = 8 * nt_idx + 2 * t + c;
+                        const int qi = r < p.rows ? r / p.g : 0;           // padding rows copy row 0's window
+                        int hi = lloc_i - 1;
+                        if (p.new_rows && pos_loc + qi < hi) hi = pos_loc + qi;
+                        const int lo = p.window > 0 ? pos_loc + qi - p.window + 1 : 0;
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const long long kv = key0 + a * 16 + g + 8 * h;
-                            if (!(kv <= lim_hi[0] && kv >= lim_lo[0])) tv[a][2 * h + 0] = -INFINITY;
-                            if (!(kv <= lim_hi[1] && kv >= lim_lo[1])) tv[a][2 * h + 1] = -INFINITY;
-                            if (kv >= lloc) vr[a][h] = 0.f;                  // never-written rows: scale may be anything
-                        }
+                        for (int a = 0; a < 2; ++a)
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const int kv = key0 + a * 16 + g + 8 * h;
+                                if (!(kv <= hi && kv >= lo)) tv[a][2 * h + c] = -INFINITY;
+                                if (kv >= lloc_i) vr[a][h] = 0.f;            // never-written rows: scale may be anything
+                            }
+                    }
                 }
                 // ---- online softmax over the 32 keys (rows of S^T): reduce across the g lanes
                 float alpha[2];
@@ -402,52 +422,47 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                         acc[a][2] *= alpha[0]; acc[a][3] *= alpha[1];
                     }
                 }
-                if (FP8) {
-                    // ---- P^T as the B operand of m16n8k32: per 16-key group pack the codes of keys
-                    // (g, g+8) of one column into 16 bits, transpose the 8x8 blocks of such units
-                    // across the warp; k-slots 4t..4t+3 then hold keys 2t, 2t+8, 2t+1, 2t+9.
-                    uint32_t ph[2], pl[2];
+                // ---- O^T[D dims, 8 columns] += V^T P^T per 16-key group; P^T as the B operand: pack the
+                // two columns of a key, transpose the 8x8 blocks across the warp
 #pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        const float y[4] = {tv[a][0] * DEC_P_SCALE, tv[a][2] * DEC_P_SCALE,      // column 2t:   keys g, g+8
-                                            tv[a][1] * DEC_P_SCALE, tv[a][3] * DEC_P_SCALE};     // column 2t+1: keys g, g+8
-                        uint32_t hi, lo;
-                        split_e4m3x4(y, hi, lo);
-                        ph[a] = movmatrix_trans(hi);
-                        pl[a] = movmatrix_trans(lo);
-                    }
-                    // ---- O^T[D dims, 8 columns] += V^T P^T
+                for (int a = 0; a < 2; ++a) {
+                    const uint32_t pb0 = movmatrix_trans(FP8 ? pack_f16x2(tv[a][0], tv[a][1]) : pack_bf16x2(tv[a][0], tv[a][1]));
+                    const uint32_t pb1 = movmatrix_trans(FP8 ? pack_f16x2(tv[a][2], tv[a][3]) : pack_bf16x2(tv[a][2], tv[a][3]));
 #pragma unroll
-                    for (int cp = 0; cp < C::NCP; ++cp) {
-                        uint32_t w[4], x[4];
-                        ldmatrix_x4_trans(w, vt + tile_off(v_row, (2 * cp) * 16));
-                        ldmatrix_x4_trans(x, vt + tile_off(v_row, (2 * cp + 1) * 16));
-                        uint32_t av[4];
-                        av[0] = prmt(w[0], w[1], 0x6240u); av[1] = prmt(x[0], x[1], 0x6240u);
-                        av[2] = prmt(w[2], w[3], 0x6240u); av[3] = prmt(x[2], x[3], 0x6240u);
-                        mma_e4m3(acc[2 * cp], av, ph[0], ph[1]);
-                        mma_e4m3(acc[2 * cp], av, pl[0], pl[1]);
-                        av[0] = prmt(w[0], w[1], 0x7351u); av[1] = prmt(x[0], x[1], 0x7351u);
-                        av[2] = prmt(w[2], w[3], 0x7351u); av[3] = prmt(x[2], x[3], 0x7351u);
-                        mma_e4m3(acc[2 * cp + 1], av, ph[0], ph[1]);
-                        mma_e4m3(acc[2 * cp + 1], av, pl[0], pl[1]);
-                    }
-                } else {
+                    for (int q = 0; q < NQ; ++q) {
+                        const uint32_t va = vt + v_lane + (((2u * q + v_chunk) ^ urr) << 4) + a * (16 * 128);
 #pragma unroll
-                    for (int a = 0; a < 2; ++a) {
-                        const uint32_t pb0 = movmatrix_trans(pack_bf16x2(tv[a][0], tv[a][1]));
-                        const uint32_t pb1 = movmatrix_trans(pack_bf16x2(tv[a][2], tv[a][3]));
-#pragma unroll
-                        for (int cp = 0; cp < C::NCP; ++cp) {
+                        for (int sg = 0; sg < NSEG; ++sg) {
+                            const int cp = 4 * sg + q;
                             uint32_t w[4];
-                            ldmatrix_x4_trans(w, vt + tile_off(a * 16 + v_row, (2 * cp + v_chunk) * 16));
-                            mma_bf16(acc[cp], w, pb0, pb1);
+                            ldmatrix_x4_trans(w, va + sg * (DEC_BN * 128));
+                            if (FP8) {
+                                // a transposed register holds dims (2g, 2g+1) of keys (2t, 2t+1): regroup to
+                                // (key 2t, key 2t+1) of dim 2g | of dim 2g+1, then e4m3 -> f16
+                                uint32_t af[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) w[e] = prmt(w[e], 0u, 0x3120u);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(w[e] & 0xffffu));
+                                mma_f16(acc[2 * cp], af, pb0, pb1);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(w[e] >> 16));
+                                mma_f16(acc[2 * cp + 1], af, pb0, pb1);
+                            } else {
+                                mma_bf16(acc[cp], w, pb0, pb1);
+                            }
                         }
                     }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_empty[s]);
+#ifndef TRB_DEC_NOLOAD
+            if (issuer && i + C::NSTAGE < my_tiles) {          // refill the stage once every slice has left it
+                if (!mbar_wait(&bar_empty[s], (i / C::NSTAGE) & 1)) break;
+                issue_tile(i + C::NSTAGE);
+            }
+#endif
         }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -459,12 +474,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
     // =============================== CTA epilogue =======================================
     // 1. merge the kw warps that share an 8-row slice (fixed order), through shared memory
-    named_barrier(1, DEC_CTHREADS);                    // every stage has been consumed
+    __syncthreads();                    // every stage has been consumed
     if (warp_on && g == 0) {
         sm_ml[(warp * 8 + 2 * t + 0) * 2 + 0] = mx[0]; sm_ml[(warp * 8 + 2 * t + 0) * 2 + 1] = ls[0];
         sm_ml[(warp * 8 + 2 * t + 1) * 2 + 0] = mx[1]; sm_ml[(warp * 8 + 2 * t + 1) * 2 + 1] = ls[1];
     }
-    named_barrier(1, DEC_CTHREADS);
+    __syncthreads();
     float *stage_acc = reinterpret_cast<float *>(smem);                // [warp][8][D + pad]
     constexpr int SROW = D + DEC_EPI_PAD;
     if (warp_on) {
@@ -473,7 +488,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         for (int c = 0; c < 2; ++c) {
             float mg = -INFINITY;
             for (int k = 0; k < p.kw; ++k) mg = fmaxf(mg, sm_ml[((k * p.nt + nt_idx) * 8 + 2 * t + c) * 2]);
-            wgt[c] = mg == -INFINITY ? 0.f : fast_exp2(mx[c] - mg) * (FP8 ? 1.f / DEC_P_SCALE : 1.f);
+            wgt[c] = mg == -INFINITY ? 0.f : fast_exp2(mx[c] - mg);
         }
 #pragma unroll
         for (int a = 0; a < C::ACC; ++a)
@@ -481,7 +496,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             for (int i = 0; i < 4; ++i)
                 stage_acc[(warp * 8 + 2 * t + (i & 1)) * SROW + acc_dim<FP8>(a, i, g)] = acc[a][i] * wgt[i & 1];
     }
-    named_barrier(1, DEC_CTHREADS);
+    __syncthreads();
     const int tid = threadIdx.x;                                       // 0..383 here
     const long long part_base = ((long long)j * p.nsplit + split) * p.rows_pad;
     for (int item = tid; item < p.nt * 8 * (D / 4); item += DEC_CTHREADS) {
@@ -508,78 +523,92 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         p.part_ml[(part_base + row) * 2 + 1] = lg;
     }
 
-    // 2. ticket: the last CTA of this kv head merges the splits
+    // 2. ticket.  The last CTA of this kv head to arrive publishes a new epoch; CTAs that arrived
+    // earlier wait for it (bounded) and then every CTA present claims output rows one at a time
+    // and merges them, so the combine runs on many SMs.  The last CTA keeps claiming until no
+    // row is left, so the result is complete even if every helper gave up waiting.
+    unsigned int *ticket = p.counters + j, *claim = p.counters + 64 + j, *seq = p.counters + 128 + j;
     __threadfence();
-    named_barrier(1, DEC_CTHREADS);
+    __syncthreads();
     if (tid == 0) {
-        const unsigned int old = atomicAdd(&p.counters[j], 1u);
-        const int last = old == (unsigned int)(active - 1);
-        if (last) p.counters[j] = 0u;                                  // ready for the next launch / replay
-        *sm_flag = last;
+        const unsigned int old = atomicAdd(ticket, 1u);
+        int state = old == (unsigned int)(active - 1) ? 2 : 1;
+        if (state == 2) {
+            *ticket = 0u;                                               // ready for the next launch / replay
+            *claim = 0u;
+            __threadfence();
+            *(volatile unsigned int *)seq = epoch + 1u;
+        } else {
+            state = 0;
+            for (int it = 0; it < 4096; ++it) {
+                if (*(volatile unsigned int *)seq == epoch + 1u) { state = 1; break; }
+                __nanosleep(100);
+            }
+        }
+        *sm_flag = state;
     }
-    named_barrier(1, DEC_CTHREADS);
-    if (!*sm_flag) return;
+    __syncthreads();
+    if (*sm_flag == 0) return;                                          // gave up waiting: the others finish the rows
     __threadfence();
 
-    // 3. tail: LSE merge over the active splits (+ extra partials), fixed order
+    // 3. tail: LSE merge of one output row per claim over the active splits (+ extra partials), in
+    // split order: thread (item, group) sums the splits of its group, the groups are added in
+    // group order through shared memory.
     const int n_parts = active + p.n_extra;
-    float *sm_w = stage_acc + DEC_CONSUMERS * 8 * SROW;               // [rows][n_parts] weights, then [rows] 1/l
-    float *sm_inv = sm_w + DEC_MAX_ROWS * (p.nsplit + 1);
-    for (int row = warp; row < p.rows; row += DEC_CONSUMERS) {
+    constexpr int ITEMS = D / 4, GROUPS = DEC_CTHREADS / ITEMS;
+    float *sm_m = reinterpret_cast<float *>(smem);                      // [n_parts]
+    float *sm_l = sm_m + (DEC_MAX_SPLITS + 4);                          // [n_parts]
+    float4 *sm_red = reinterpret_cast<float4 *>(sm_l + (DEC_MAX_SPLITS + 4));   // [GROUPS][ITEMS]
+    int *sm_claim = sm_flag + 1;
+    const int item = tid % ITEMS, grp = tid / ITEMS, d4 = item * 4;
+    for (;;) {
+        __syncthreads();
+        if (tid == 0) *sm_claim = (int)atomicAdd(claim, 1u);
+        __syncthreads();
+        const int row = *sm_claim;
+        if (row >= p.rows) break;
         const int qi = row / p.g, hq = j * p.g + row % p.g;
         const long long grow = (long long)qi * p.hq + hq;
-        float mmax = -INFINITY;
-        for (int s = lane; s < n_parts; s += 32) {
-            const float ms = s < active ? __ldcg(&p.part_ml[(((long long)j * p.nsplit + s) * p.rows_pad + row) * 2])
-                                        : p.extra_ml[(grow * p.n_extra + (s - active)) * 2];
-            mmax = fmaxf(mmax, ms);
+        for (int sp = tid; sp < n_parts; sp += DEC_CTHREADS) {
+            float2 v;
+            if (sp < active) v = __ldcg(reinterpret_cast<const float2 *>(&p.part_ml[(((long long)j * p.nsplit + sp) * p.rows_pad + row) * 2]));
+            else v = *reinterpret_cast<const float2 *>(&p.extra_ml[(grow * p.n_extra + (sp - active)) * 2]);
+            sm_m[sp] = v.x; sm_l[sp] = v.y;
         }
+        __syncthreads();
+        float mmax = -INFINITY, lsum = 0.f;
+        for (int sp = lane; sp < n_parts; sp += 32) mmax = fmaxf(mmax, sm_m[sp]);
         mmax = warp_max(mmax);
-        float lsum = 0.f;
-        for (int s = lane; s < n_parts; s += 32) {
-            float ms, lsv;
-            if (s < active) {
-                const float2 v = __ldcg(reinterpret_cast<const float2 *>(&p.part_ml[(((long long)j * p.nsplit + s) * p.rows_pad + row) * 2]));
-                ms = v.x; lsv = v.y;
-            } else {
-                ms = p.extra_ml[(grow * p.n_extra + (s - active)) * 2];
-                lsv = p.extra_ml[(grow * p.n_extra + (s - active)) * 2 + 1];
-            }
-            const float w = ms == -INFINITY ? 0.f : fast_exp2(ms - mmax);
-            sm_w[row * n_parts + s] = w;
-            lsum += w * lsv;
-        }
+        for (int sp = lane; sp < n_parts; sp += 32) lsum += sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax) * sm_l[sp];
         lsum = warp_sum(lsum);
-        if (lane == 0) {
-            sm_inv[row] = 1.f / lsum;
-            if (p.shard_ml) { p.shard_ml[grow * 2] = mmax; p.shard_ml[grow * 2 + 1] = lsum; }
-        }
-    }
-    named_barrier(1, DEC_CTHREADS);
-    for (int item = tid; item < p.rows * (D / 4); item += DEC_CTHREADS) {
-        const int row = item / (D / 4), d4 = (item % (D / 4)) * 4;
-        const int qi = row / p.g, hq = j * p.g + row % p.g;
-        const long long grow = (long long)qi * p.hq + hq;
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float *wr = sm_w + row * n_parts;
         const float *pa = p.part_acc + ((long long)j * p.nsplit * p.rows_pad + row) * D + d4;
         const long long pstride = (long long)p.rows_pad * D;
 #pragma unroll 8
-        for (int s = 0; s < active; ++s) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(pa + s * pstride));
-            const float w = wr[s];
+        for (int sp = grp; sp < active; sp += GROUPS) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride));
+            const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
             o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
         }
-        for (int e = 0; e < p.n_extra; ++e) {
-            const float4 v = *reinterpret_cast<const float4 *>(&p.extra_acc[(grow * p.n_extra + e) * D + d4]);
-            const float w = wr[active + e];
-            o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+        if (grp == 0)
+            for (int e = 0; e < p.n_extra; ++e) {
+                const float4 v = *reinterpret_cast<const float4 *>(&p.extra_acc[(grow * p.n_extra + e) * D + d4]);
+                const float w = sm_m[active + e] == -INFINITY ? 0.f : fast_exp2(sm_m[active + e] - mmax);
+                o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+            }
+        sm_red[grp * ITEMS + item] = o;
+        __syncthreads();
+        if (grp != 0) continue;
+        for (int k = 1; k < GROUPS; ++k) {
+            const float4 v = sm_red[k * ITEMS + item];
+            o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
         }
         if (p.shard_acc) {
             *reinterpret_cast<float4 *>(&p.shard_acc[grow * D + d4]) = o;
+            if (item == 0) { p.shard_ml[grow * 2] = mmax; p.shard_ml[grow * 2 + 1] = lsum; }
             continue;
         }
-        const float inv = sm_inv[row];
+        const float inv = 1.f / lsum;
         float r[4] = {o.x * inv, o.y * inv, o.z * inv, o.w * inv};
         __nv_bfloat16 ob[4];
 #pragma unroll
@@ -697,7 +726,7 @@ struct WorkspaceLayout {
 static WorkspaceLayout workspace_layout(int hkv, int nsplit, int rows_pad, int d) {
     WorkspaceLayout w;
     w.counters = 0;
-    w.ml = 256;
+    w.ml = 1024;
     w.acc = align_up(w.ml + (size_t)hkv * nsplit * rows_pad * 2 * sizeof(float), 256);
     w.total = w.acc + (size_t)hkv * nsplit * rows_pad * d * sizeof(float);
     return w;
@@ -745,7 +774,7 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     if (a->window < 0) return TRB_E_ARG;
     if (c.ring > 0 && (c.ring % DEC_BN)) return TRB_E_UNSUPPORTED;
     if (c.ring > 0 && a->window + a->m > c.ring) return TRB_E_CAPACITY;
-    if (c.max_len >= (1LL << 31)) return TRB_E_UNSUPPORTED;
+    if (c.max_len >= (1LL << 31) - 64 || c.shard_lo < 0 || c.shard_lo >= (1LL << 40)) return TRB_E_UNSUPPORTED;
     if ((rc = check_cursor(&a->pos))) return rc;
     if (((uintptr_t)a->q | (uintptr_t)a->out | (uintptr_t)a->workspace | (uintptr_t)a->partial_acc | (uintptr_t)a->extra_acc) & 15)
         return TRB_E_ALIGN;
