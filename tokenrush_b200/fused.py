@@ -132,7 +132,7 @@ def attn_prep(qkv, q_norm_w, k_norm_w, cos, sin, pos_t, k_cache, v_cache, cfg, k
 # ------------------------------------------------------------------------------ decode
 
 def _decode(q, k_cache, v_cache, pos, HQ, HKV, D, k_scale, v_scale, *, gate=None, gate_rs=0, gate_hs=0, new_rows=1,
-            window=0, ring=0, shard_lo=None, extra=None, partial=False, scale=None):
+            window=0, ring=0, shard_lo=None, extra=None, partial=False, scale=None, out=None):
     _need_cuda(q)
     if q.dtype != torch.bfloat16 or not q.is_contiguous():
         raise ValueError("q must be contiguous bf16 [M, HQ*D]")
@@ -156,19 +156,23 @@ def _decode(q, k_cache, v_cache, pos, HQ, HKV, D, k_scale, v_scale, *, gate=None
         a.partial_ml, a.partial_acc = ml.data_ptr(), acc.data_ptr()
         out = (ml, acc)
     else:
-        out = torch.empty(M, HQ * D, device=q.device, dtype=q.dtype)
+        if out is None:
+            out = torch.empty(M, HQ * D, device=q.device, dtype=q.dtype)
+        elif out.dtype != torch.bfloat16 or not out.is_contiguous() or out.numel() != M * HQ * D:
+            raise ValueError("out must be contiguous bf16 [M, HQ*D]")
         a.out = out.data_ptr()
     L.check(L.lib().trb_attn_decode(C.byref(cache), C.byref(a), _stream()), "trb_attn_decode")
     return out
 
 
 def attn_decode_fused(q, qkv, k_cache, v_cache, pos_t, cfg, k_scale=None, v_scale=None, NSPLIT=32, BLOCK_N=32,
-                      shard_lo=None, partial: bool = False):
+                      shard_lo=None, partial: bool = False, out=None):
     """q [M, HQ*D] (from attn_prep) for the M new tokens at pos.., qkv [M, ..] (for the gates;
     None: ungated) -> gated attention output [M, HQ*D]; query i sees cache rows <= pos + i.
     NSPLIT / BLOCK_N are accepted for signature compatibility; the split count is chosen
     from the SM count and the split ranges from the live length on the device.
-    partial=True (sequence shards): returns this cache's (ml [M*HQ, 2], acc [M*HQ, D])."""
+    partial=True (sequence shards): returns this cache's (ml [M*HQ, 2], acc [M*HQ, D]).
+    out (optional): a preallocated [M, HQ*D] bf16 tensor to write instead of a new one."""
     HQ, HKV, D = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
     gate = None
     rs = hs = 0
@@ -176,7 +180,7 @@ def attn_decode_fused(q, qkv, k_cache, v_cache, pos_t, cfg, k_scale=None, v_scal
         _need_cuda(qkv)
         gate, rs, hs = qkv.data_ptr() + D * qkv.element_size(), qkv.stride(0), 2 * D
     return _decode(q, k_cache, v_cache, pos_t, HQ, HKV, D, k_scale, v_scale, gate=gate, gate_rs=rs, gate_hs=hs,
-                   new_rows=1, shard_lo=shard_lo, partial=partial)
+                   new_rows=1, shard_lo=shard_lo, partial=partial, out=out)
 
 
 def attn_window_block(q, k_cache, v_cache, pos_t, k_blk, v_blk, HQ, HKV, D, window, NSPLIT=15, BLOCK_N=32, ring=0):

@@ -1,0 +1,146 @@
+"""Sequence-sharded decode over the GPUs of one box (one process per GPU).
+
+The reference is single-GPU; its split kernel already reduces (max, sum, acc) triples over
+32 key ranges of one cache (tokenrush/fused.py:417-420 write, :432-438 merge).  Here the same
+reduction runs one level up: GPU g owns positions [g*S/G, (g+1)*S/G) of every layer's cache,
+scans its live rows, and the per-GPU partials are merged in rank order on every GPU.
+
+Two exchange paths:
+  * "p2p"  (default): plain peer stores over NVLink into exchange buffers shared with CUDA IPC
+    handles, one fused push + bounded wait + merge kernel per layer (trb_p2p_merge);
+  * "nccl": torch.distributed all_gather of the partials, then trb_lse_merge.  The baseline.
+Both produce the same bits: the merge order is the rank order.
+
+The appended row is written by the GPU that owns its position; every rank issues the same
+launches, the kernels skip positions they do not hold, so one captured graph is valid on
+all ranks.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+from . import fused
+from .state import State
+
+
+def shard_range(rank: int, world: int, window: int) -> tuple[int, int]:
+    """Contiguous equal shards of a window of `window` positions."""
+    if window % world:
+        raise ValueError("window must be a multiple of the number of GPUs")
+    per = window // world
+    return rank * per, (rank + 1) * per
+
+
+def owner_of(pos: int, world: int, window: int) -> int:
+    """Rank that holds position pos; positions past the window stay with the last rank."""
+    return min(pos // (window // world), world - 1)
+
+
+def live_rows(rank: int, world: int, window: int, live: int, headroom: int = 0) -> int:
+    """Rows of this rank's shard that are live when the sequence holds `live` positions."""
+    lo, hi = shard_range(rank, world, window)
+    cap = hi - lo + (headroom if rank == world - 1 else 0)
+    return max(0, min(live - lo, cap))
+
+
+class ShardedState(State):
+    """One rank's shard of the KV state.  The last rank carries `headroom` extra rows so that
+    the sequence can grow past the window."""
+
+    def __init__(self, cfg, window: int, rank: int, world: int, device="cuda", kv_dtype=torch.float8_e4m3fn,
+                 headroom: int = 0, pos_dtype=torch.long):
+        lo, hi = shard_range(rank, world, window)
+        rows = hi - lo + (headroom if rank == world - 1 else 0)
+        super().__init__(cfg, rows, device, kv_dtype=kv_dtype, shard_lo=lo, pos_dtype=pos_dtype)
+        self.rank, self.world, self.window = rank, world, window
+
+
+class PartialExchange:
+    """Exchange buffers for the per-layer merge of (max, sum, acc) partials of `rows` query rows."""
+
+    def __init__(self, rows: int, d: int, hq: int, group=None, mode: str = "p2p", device=None):
+        import torch.distributed as dist
+        self.rows, self.d, self.hq, self.mode = rows, d, hq, mode
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._local = None
+        self._peers = []
+        if mode == "p2p":
+            lib = L.lib()
+            nbytes = lib.trb_p2p_exchange_bytes(self.world, rows, d)
+            if nbytes == 0:
+                raise ValueError("unsupported exchange geometry")
+            local = C.c_void_p()
+            handle = C.create_string_buffer(L.IPC_HANDLE_BYTES)
+            L.check(lib.trb_p2p_create(nbytes, C.byref(local), handle), "trb_p2p_create")
+            self._local = local.value
+            handles = [None] * self.world
+            if self.world > 1:
+                dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            else:
+                handles[0] = bytes(handle.raw)
+            ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    ptrs.append(self._local)
+                else:
+                    peer = C.c_void_p()
+                    L.check(lib.trb_p2p_open(handles[r], C.byref(peer)), "trb_p2p_open")
+                    self._peers.append(peer.value)
+                    ptrs.append(peer.value)
+            self.xchg = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
+            self.seq = torch.zeros(1, dtype=torch.int32, device=self.device)
+            if self.world > 1:
+                dist.barrier(group=group)
+        elif mode != "nccl":
+            raise ValueError("mode must be 'p2p' or 'nccl'")
+
+    def merge(self, ml: torch.Tensor, acc: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+        """ml [rows, 2], acc [rows, d] of this rank -> merged attention output [rows, d] bf16
+        (identical on every rank)."""
+        if out is None:
+            out = torch.empty(self.rows, self.d, device=acc.device, dtype=torch.bfloat16)
+        if self.mode == "p2p":
+            a = L.P2PMergeArgs(self.xchg.data_ptr(), self.world, self.rank, self.seq.data_ptr(), ml.data_ptr(), acc.data_ptr(),
+                               self.rows, self.d, self.hq, 0, out.data_ptr(), None, 0, 0)
+            L.check(L.lib().trb_p2p_merge(C.byref(a), torch.cuda.current_stream().cuda_stream), "trb_p2p_merge")
+            return out
+        import torch.distributed as dist
+        mls = torch.empty(self.world, self.rows, 2, device=acc.device, dtype=torch.float32)
+        accs = torch.empty(self.world, self.rows, self.d, device=acc.device, dtype=torch.float32)
+        if self.world > 1:
+            dist.all_gather_into_tensor(mls, ml.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(accs, acc.contiguous(), group=self.group)
+        else:
+            mls[0], accs[0] = ml, acc
+        res = fused.lse_merge(mls, accs, hq=self.hq)
+        if out is not None:
+            out.view(self.rows, self.d).copy_(res)
+            return out
+        return res
+
+    def close(self):
+        if self.mode == "p2p" and self._local is not None:
+            torch.cuda.synchronize()
+            lib = L.lib()
+            for p in self._peers:
+                lib.trb_p2p_close(p)
+            lib.trb_p2p_destroy(self._local)
+            self._local, self._peers = None, []
+
+
+def sharded_decode_layer(state: ShardedState, slot: int, q, k_new, v_new, cfg, xchg: PartialExchange, out=None) -> torch.Tensor:
+    """One layer of a sharded decode step: append the new rows (only the owner writes), scan
+    this shard, exchange and merge.  q [M, HQ*D]; k_new, v_new [HKV, M, D].  Returns [M, HQ*D]."""
+    ks = state.k_scale[slot] if state.fp8 else None
+    vs = state.v_scale[slot] if state.fp8 else None
+    fused.kv_append(k_new, v_new, state.k[slot], state.v[slot], state.pos_t, ks, vs, shard_lo=state.shard_lo)
+    ml, acc = fused.attn_decode_fused(q, None, state.k[slot], state.v[slot], state.pos_t, cfg, ks, vs,
+                                      shard_lo=state.shard_lo, partial=True)
+    res = xchg.merge(ml, acc, out=out)
+    return res.view(q.shape[0], -1)
