@@ -134,6 +134,32 @@ typedef struct trb_decode_args {
 size_t trb_decode_workspace_bytes(int32_t hq, int32_t hkv, int32_t d, int32_t m);
 int    trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t *args, trb_stream_t stream);
 
+/* ------------------------------------------------------------------ decode without a workspace
+ * No counterpart in the reference (its wrappers allocate the split partials with torch.empty on
+ * every call).
+ *
+ * For callers that cannot give the library device memory at the point of the call: a host
+ * runtime whose device memory belongs to its own arena and has no allocation hook for plugins,
+ * or a thin FFI binding that only forwards the buffers it received and has no way to create
+ * one more.  Same arguments and result as
+ * trb_attn_decode, except that args->workspace / workspace_bytes are ignored: the split
+ * partials and tickets live in a file-scope device array of TRB_STATIC_SCRATCH_BYTES that is
+ * part of the library image (every GPU that loads the library holds it until the process
+ * exits).  The call itself allocates and frees nothing.
+ *
+ *   - Limit: the scratch need of the geometry, trb_decode_workspace_bytes(hq, hkv, d, m), must
+ *     not exceed TRB_STATIC_SCRATCH_BYTES (4 MiB: up to m = 4 rows for 24 query / 4 KV heads
+ *     x 256); larger calls return TRB_E_SCRATCH_LIMIT and launch nothing.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current) and keeps it; make that first call before any stream capture begins.
+ *   - All calls share the one array, which keeps the previous call's contents; the call clears
+ *     the small header that must start at zero (stream-ordered) and every partial is rewritten
+ *     before it is read.  Two calls whose kernels overlap on the GPU (different streams, or
+ *     several host threads) race on it: order them on one stream. */
+#define TRB_STATIC_SCRATCH_BYTES (4u << 20)
+#define TRB_E_SCRATCH_LIMIT (-7)
+int trb_attn_decode_static(const trb_cache_t *cache, const trb_decode_args_t *args, trb_stream_t stream);
+
 /* Softmax statistics of the b in-step block keys, all visible to all b queries, written as
  * one extra partial for trb_attn_decode.  Replaces _attn_block_kernel
  * (tokenrush/fused.py:575-597).  q [b, hq*d], k_blk / v_blk [hkv, b, d] bf16. */

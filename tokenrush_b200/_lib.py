@@ -61,6 +61,7 @@ SIGNATURES = {
                                 C.c_int32, C.c_float, C.c_int32, C.c_int32, C.POINTER(Cursor), C.c_void_p, C.c_void_p]),
     "trb_decode_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "trb_attn_decode": (C.c_int, [C.POINTER(Cache), C.POINTER(DecodeArgs), C.c_void_p]),
+    "trb_attn_decode_static": (C.c_int, [C.POINTER(Cache), C.POINTER(DecodeArgs), C.c_void_p]),
     "trb_attn_block_partial": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                          C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]),
     "trb_lse_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,

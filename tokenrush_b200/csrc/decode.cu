@@ -835,3 +835,54 @@ extern "C" int trb_lse_merge(const float *ml, const float *acc, int32_t n_parts,
     TRB_CUDA_CHECK(cudaGetLastError());
     return TRB_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode without caller-provided scratch.
+//
+// Some callers cannot hand the library a scratch buffer because they cannot allocate device
+// memory at the point of the call: a host runtime that owns all device memory through its own
+// arena and exposes no allocation hook to plugins, or a thin FFI binding (cgo / JNI style) that
+// only forwards the buffers it was given.  For them the split-partial scratch lives in the array below, which is part of the
+// library image: every GPU that loads the library holds TRB_STATIC_SCRATCH_BYTES until the
+// process exits.
+//
+// The array's name is only a handle on the host side; the device address is looked up once
+// per device with cudaGetSymbolAddress (with that device current) and handed to the kernel.
+static __device__ __align__(256) unsigned char g_static_scratch[TRB_STATIC_SCRATCH_BYTES];
+
+namespace trb {
+static std::mutex g_static_mu;
+static void *g_static_ptr[64] = {};
+
+static int static_scratch_ptr(void **out) {
+    int dev = 0;
+    TRB_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return TRB_E_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void *ptr = nullptr;
+        TRB_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        g_static_ptr[dev] = ptr;
+    }
+    *out = g_static_ptr[dev];
+    return TRB_OK;
+}
+}  // namespace trb
+
+extern "C" int trb_attn_decode_static(const trb_cache_t *cache, const trb_decode_args_t *args, trb_stream_t stream) {
+    if (!cache || !args) return TRB_E_ARG;
+    if (cache->hkv < 1 || args->hq < 1 || args->m < 1 || args->hq % cache->hkv) return TRB_E_ARG;
+    const size_t need = trb_decode_workspace_bytes(args->hq, cache->hkv, cache->d, args->m);
+    if (need == 0) return TRB_E_UNSUPPORTED;
+    if (need > TRB_STATIC_SCRATCH_BYTES) return TRB_E_SCRATCH_LIMIT;
+    void *scratch = nullptr;
+    int rc = static_scratch_ptr(&scratch);
+    if (rc) return rc;
+    // The array keeps whatever the previous call left.  Only the header (tickets, claims, epochs)
+    // has to start from zero; the partials are fully rewritten before they are read.
+    TRB_CUDA_CHECK(cudaMemsetAsync(scratch, 0, 1024, (cudaStream_t)stream));
+    trb_decode_args_t a = *args;
+    a.workspace = scratch;
+    a.workspace_bytes = TRB_STATIC_SCRATCH_BYTES;
+    return trb_attn_decode(cache, &a, stream);
+}

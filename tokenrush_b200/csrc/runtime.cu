@@ -25,6 +25,9 @@ extern "C" const char *trb_strerror(int code) {
         case TRB_E_CUDA: return g_last_cuda[0] ? g_last_cuda : "CUDA call failed";
         case TRB_E_UNSUPPORTED: return "geometry outside what the kernels are built for";
         case TRB_E_DEVICE: return "device status word is non-zero";
+        case TRB_E_SCRATCH_LIMIT:
+            return "trb_attn_decode_static: this geometry needs more split scratch than the built-in "
+                   "TRB_STATIC_SCRATCH_BYTES (4 MiB); call trb_attn_decode with a caller-provided workspace";
         default: return "unknown error";
     }
 }
