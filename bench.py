@@ -286,9 +286,14 @@ def run_product(args):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        if xchg is not None:
-            xchg.close()
-        dist.destroy_process_group()
+        # Leave without tearing NCCL down: destroying a communicator whose collectives were captured
+        # into a still-live CUDA graph can block forever.  Everything is flushed and every rank has
+        # finished its timed work before the processes exit.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def run_cpu_sample(ctx: int, m: int, budget_s: float = 15.0):
