@@ -1,0 +1,89 @@
+"""GPU parity of the chunked prefill attention (tcgen05 kernel, through the C ABI) against the
+reference's golden vectors and the CPU oracle; new rows are appended (FP8) first and attended in
+quantised form, as the reference does (tokenrush/model.py:136-137)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import kv_oracle as O
+from _util import HQ, HKV, D, to_dev, f32_of, assert_attn_close, oracle_state_from
+
+pytestmark = pytest.mark.gpu
+F8 = torch.float8_e4m3fn
+
+
+@pytest.fixture(scope="module")
+def tb():
+    import tokenrush_b200 as tb
+    return tb
+
+
+def _prefill(tb, cfg, st, qb, kb, vb, pos):
+    """append the chunk at pos (host int, as the reference's eager prefill) then attend."""
+    tb.fused.kv_write_prefill(to_dev(kb), to_dev(vb), st, 0, pos)
+    return tb.fused.attn_prefill_fused(to_dev(qb), st.k[0], st.v[0], pos, cfg, st.k_scale[0], st.v_scale[0])
+
+
+def test_prefill_matches_reference_golden(tb, golden_dir):
+    z = np.load(os.path.join(golden_dir, "prefill.npz"))
+    pos, T, rows = int(z["pos"]), int(z["T"]), z["rows"]
+    kb, vb = O.seeded_bf16(501, HKV, pos + T, D), O.seeded_bf16(502, HKV, pos + T, D)
+    qb = O.seeded_bf16(503, T, HQ, D)
+    cfg = tb.AttnConfig(n_attn=1)
+    st = tb.State(cfg, 128, "cuda", kv_dtype=F8)
+    tb.fused.kv_write_prefill(to_dev(kb[:, :pos]), to_dev(vb[:, :pos]), st, 0, 0)
+    for _ in range(2):
+        o = _prefill(tb, cfg, st, qb, kb[:, pos:], vb[:, pos:], pos)
+        assert_attn_close(f32_of(o)[rows], z["out"], "prefill golden")
+    assert tb._lib.device_status() == 0
+
+
+@pytest.mark.parametrize("pos,T", [(0, 1), (0, 64), (0, 130), (37, 150), (300, 300), (1000, 257)])
+def test_prefill_vs_oracle(tb, pos, T):
+    """Chunks that start at 0 and mid-cache, sizes around the 128-row query block and the
+    64-key tile; every row is compared."""
+    kb, vb = O.seeded_bf16(601 + pos, HKV, pos + T, D), O.seeded_bf16(602 + pos, HKV, pos + T, D)
+    qb = O.seeded_bf16(603 + T, T, HQ, D)
+    cfg = tb.AttnConfig(n_attn=1)
+    st = tb.State(cfg, pos + T + 40, "cuda", kv_dtype=F8)
+    if pos:
+        tb.fused.kv_write_prefill(to_dev(kb[:, :pos]), to_dev(vb[:, :pos]), st, 0, 0)
+    o = _prefill(tb, cfg, st, qb, kb[:, pos:], vb[:, pos:], pos)
+    ref = oracle_state_from(st)
+    kd, vd = ref.dequant(0, pos + T)
+    want = O.attn_prefill(O.bf16_bits_to_f32(qb), kd, vd, pos)
+    assert_attn_close(f32_of(o), want, f"pos={pos} T={T}")
+    assert tb._lib.device_status() == 0
+
+
+def test_prefill_then_decode_consistency(tb):
+    """The last row of a prefill chunk equals a 1-row decode at the same position over the same
+    cache (the reference's tests/test_ops.py:139-146 self-consistency, here across two kernels)."""
+    pos, T = 200, 96
+    kb, vb = O.seeded_bf16(701, HKV, pos + T, D), O.seeded_bf16(702, HKV, pos + T, D)
+    qb = O.seeded_bf16(703, T, HQ, D)
+    cfg = tb.AttnConfig(n_attn=1)
+    st = tb.State(cfg, 512, "cuda", kv_dtype=F8)
+    tb.fused.kv_write_prefill(to_dev(kb[:, :pos]), to_dev(vb[:, :pos]), st, 0, 0)
+    o = f32_of(_prefill(tb, cfg, st, qb, kb[:, pos:], vb[:, pos:], pos))
+    st.set_pos(pos + T - 1)
+    od = tb.fused.attn_decode_fused(to_dev(qb[T - 1:T]).reshape(1, -1), None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0], st.v_scale[0])
+    a, b = o[T - 1].reshape(-1), f32_of(od).reshape(-1)
+    assert np.linalg.norm(a - b) / np.linalg.norm(b) < 5e-3
+
+
+def test_prefill_peaked_scores(tb):
+    """q scaled x8: peaked softmax, running maximum changes often (exercises the correction of O)."""
+    pos, T = 64, 200
+    kb, vb = O.seeded_bf16(801, HKV, pos + T, D), O.seeded_bf16(802, HKV, pos + T, D)
+    qb = O.f32_to_bf16_bits(O.bf16_bits_to_f32(O.seeded_bf16(803, T, HQ, D)) * 8.0)
+    cfg = tb.AttnConfig(n_attn=1)
+    st = tb.State(cfg, 512, "cuda", kv_dtype=F8)
+    tb.fused.kv_write_prefill(to_dev(kb[:, :pos]), to_dev(vb[:, :pos]), st, 0, 0)
+    o = _prefill(tb, cfg, st, qb, kb[:, pos:], vb[:, pos:], pos)
+    ref = oracle_state_from(st)
+    kd, vd = ref.dequant(0, pos + T)
+    want = O.attn_prefill(O.bf16_bits_to_f32(qb), kd, vd, pos)
+    assert_attn_close(f32_of(o), want, "peaked prefill")

@@ -1,8 +1,409 @@
-// Chunked prefill attention over the FP8 cache (placeholder until the tcgen05 kernel lands).
+// Chunked prefill attention over the FP8 KV cache on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory).
+//
+// One CTA per (128-query block, query head).  Keys stream in tiles of 64 through a 3-stage TMA
+// ring; per tile
+//     S[128 x 64]   = (Qhi + Qlo) K^T         tcgen05.mma kind::f8f6f4, K straight from the TMA tile
+//     P             = exp2(S * k_scale * c + log2 v_scale - m)     128 threads, one query row each
+//     O[128 x 256] += (Phi + Plo) V           tcgen05.mma, V as an MN-major operand, same tile
+// The e4m3 codes of the cache feed the tensor cores unconverted.  The bf16 queries and the fp32
+// probabilities are each split into two e4m3 terms (x ~= hi + lo: 8 significant bits, what bf16
+// carries), so every product is exact and accumulation is fp32 in tensor memory; at the FP8 rate
+// the two terms cost what one bf16 pass would.  Per-key scales never touch the codes: the K scale
+// multiplies the fp32 score, the V scale is moved into the exponent of the probability.
+//
+// Warp roles: warps 0-3 softmax / correction / epilogue (thread = query row = TMEM lane),
+// warp 4 TMA producer, warp 5 MMA issuer.  Every wait is bounded.
 #include "common.cuh"
+#include "tmap.h"
+
+namespace trb {
+
+constexpr int PF_BM = 128;              // queries per CTA
+constexpr int PF_BN = 64;               // keys per tile
+constexpr int PF_D = 256;               // head dim (bytes per e4m3 row)
+constexpr int PF_STAGES = 3;
+constexpr int PF_THREADS = 192;
+constexpr int PF_TILE = PF_BN * PF_D;   // bytes of one K or V tile
+constexpr int PF_Q_BYTES = PF_BM * PF_D;               // one e4m3 copy of the query block
+constexpr int PF_P_BYTES = PF_BM * 128;                // [128 rows][hi 64 B | lo 64 B]
+constexpr int PF_OFF_Q = 0;                            // Qhi, Qlo
+constexpr int PF_OFF_KV = 2 * PF_Q_BYTES;              // stages of (K tile, V tile)
+constexpr int PF_OFF_P = PF_OFF_KV + PF_STAGES * 2 * PF_TILE;
+constexpr int PF_OFF_SC = PF_OFF_P + PF_P_BYTES;       // [stages][2][64] floats
+constexpr int PF_OFF_BAR = PF_OFF_SC + PF_STAGES * 2 * PF_BN * 4;
+constexpr int PF_SMEM = PF_OFF_BAR + 256 + 1024;
+constexpr int PF_TMEM_COLS = 512;
+constexpr int PF_TMEM_S = 0;            // S: columns [0, 64)
+constexpr int PF_TMEM_O = 256;          // O: columns [256, 512)
+
+struct PrefillParams {
+    const __nv_bfloat16 *q;
+    __nv_bfloat16 *out;
+    const float *ks, *vs;
+    int t, hq, hkv, g;
+    long long pos, max_len;
+    float scale_log2;
+};
+
+// ---- tcgen05 wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// UMMA shared-memory descriptor, 128-byte swizzle, version 1 (sm_100).
+// K-major:  rows of 128 bytes, 8-row atoms SBO apart.  MN-major: 128-byte chunks of the MN
+// extent LBO apart, 8-row (K) atoms SBO apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;          // descriptor version
+    d |= (uint64_t)2 << 61;          // SWIZZLE_128B
+    return d;
+}
+// instruction descriptor: fp32 accumulate, e4m3 x e4m3, M = 128
+__host__ __device__ constexpr uint32_t umma_idesc_f8(int n, bool b_mn_major) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(PF_BM >> 4) << 24);
+}
+
+// four fp32 -> (hi codes, lo codes) as in hi + lo ~= x
+__device__ __forceinline__ void pf_split4(const float (&x)[4], uint32_t &hi, uint32_t &lo) {
+    const __nv_fp8x2_storage_t h01 = __nv_cvt_float2_to_fp8x2(make_float2(x[0], x[1]), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t h23 = __nv_cvt_float2_to_fp8x2(make_float2(x[2], x[3]), __NV_SATFINITE, __NV_E4M3);
+    const float2 f01 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(h01, __NV_E4M3)));
+    const float2 f23 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(h23, __NV_E4M3)));
+    const __nv_fp8x2_storage_t l01 = __nv_cvt_float2_to_fp8x2(make_float2(x[0] - f01.x, x[1] - f01.y), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t l23 = __nv_cvt_float2_to_fp8x2(make_float2(x[2] - f23.x, x[3] - f23.y), __NV_SATFINITE, __NV_E4M3);
+    hi = (uint32_t)h01 | ((uint32_t)h23 << 16);
+    lo = (uint32_t)l01 | ((uint32_t)l23 << 16);
+}
+
+// byte offset of (row, byte) in a [rows][128 B] block with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t byte) {
+    return row * 128u + ((((byte >> 4) ^ (row & 7u)) & 7u) << 4) + (byte & 15u);
+}
+
+__global__ void __launch_bounds__(PF_THREADS, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+    extern __shared__ uint8_t pf_smem_raw[];
+    uint8_t *smem = pf_smem_raw + ((1024u - (smem_u32(pf_smem_raw) & 1023u)) & 1023u);
+    float *sm_sc = reinterpret_cast<float *>(smem + PF_OFF_SC);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + PF_OFF_BAR);
+    uint64_t *kv_full = bars, *kv_free = bars + PF_STAGES;
+    uint64_t *s_full = bars + 2 * PF_STAGES, *s_free = s_full + 1, *p_full = s_full + 2, *o_done = s_full + 3;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * PF_STAGES + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = blockIdx.x, h = blockIdx.y, j = h / p.g;
+    const int q0 = qb * PF_BM;
+    const int rows_here = p.t - q0 < PF_BM ? p.t - q0 : PF_BM;
+    // keys below `hi` can be seen by some row of this block
+    const long long hi = p.pos + q0 + rows_here;
+    const int n_tiles = (int)((hi + PF_BN - 1) / PF_BN);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PF_STAGES; ++s) { mbar_init(&kv_full[s], 33u); mbar_init(&kv_free[s], 1u); }
+        mbar_init(s_full, 1u); mbar_init(s_free, 4u); mbar_init(p_full, 4u); mbar_init(o_done, 1u);
+        mbar_fence_init();
+        tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+    }
+    if (warp == 0) { tmem_alloc(tmem_slot, PF_TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 4) {
+        // ================================ TMA producer ================================
+        for (int i = 0; i < n_tiles; ++i) {
+            const int s = i % PF_STAGES;
+            if (i >= PF_STAGES && !mbar_wait(&kv_free[s], ((i / PF_STAGES) & 1) ^ 1)) break;
+            const int row0 = i * PF_BN;
+            uint8_t *kt = smem + PF_OFF_KV + s * 2 * PF_TILE, *vt = kt + PF_TILE;
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&kv_full[s], 2 * PF_TILE);
+#pragma unroll
+                for (int sg = 0; sg < 2; ++sg) {
+                    tma_load_4d(kt + sg * (PF_BN * 128), &tm_k, &kv_full[s], 0, sg, row0, j);
+                    tma_load_4d(vt + sg * (PF_BN * 128), &tm_v, &kv_full[s], 0, sg, row0, j);
+                }
+            }
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const long long r = (long long)row0 + lane + 32 * hh;
+                const bool ok = r < p.max_len;
+                const long long off = (long long)j * p.max_len + (ok ? r : 0);
+                cp_async_4(&sm_sc[(s * 2 + 0) * PF_BN + lane + 32 * hh], p.ks + off, ok ? 4u : 0u);
+                cp_async_4(&sm_sc[(s * 2 + 1) * PF_BN + lane + 32 * hh], p.vs + off, ok ? 4u : 0u);
+            }
+            cp_async_mbar_arrive_noinc(&kv_full[s]);
+        }
+    } else if (warp == 5) {
+        // ================================ MMA issuer ==================================
+        // the query block must be in shared memory first (written by warps 0-3 before p_full's
+        // very first phase is used as "Q ready": they arrive on s_free once at start)
+        const uint32_t q_hi = smem_u32(smem + PF_OFF_Q), q_lo = q_hi + PF_Q_BYTES;
+        const uint32_t p_sm = smem_u32(smem + PF_OFF_P);
+        constexpr uint32_t IDESC_QK = umma_idesc_f8(PF_BN, false), IDESC_PV = umma_idesc_f8(PF_D, true);
+        bool ok = mbar_wait(s_free, 0);                                       // Q staged, S free
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int s = i % PF_STAGES;
+            const uint32_t kt = smem_u32(smem + PF_OFF_KV + s * 2 * PF_TILE), vt = kt + PF_TILE;
+            if (!(ok = mbar_wait(&kv_full[s], (i / PF_STAGES) & 1))) break;
+            if (i > 0 && !(ok = mbar_wait(s_free, i & 1))) break;               // softmax has read S of tile i-1
+            tc_fence_after();
+            if (lane == 0) {
+                // S = Qhi K^T + Qlo K^T : 2 column blocks x 4 k-steps of 32 bytes, hi then lo
+#pragma unroll
+                for (int term = 0; term < 2; ++term)
+#pragma unroll
+                    for (int sg = 0; sg < 2; ++sg)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t a = umma_desc((term ? q_lo : q_hi) + sg * (PF_BM * 128) + k * 32, 16, 1024);
+                            const uint64_t b = umma_desc(kt + sg * (PF_BN * 128) + k * 32, 16, 1024);
+                            tc_mma_f8(tmem + PF_TMEM_S, a, b, IDESC_QK, (term | sg | k) ? 1u : 0u);
+                        }
+                tc_commit(s_full);
+            }
+            __syncwarp();
+            if (!(ok = mbar_wait(p_full, i & 1))) break;                        // P of tile i staged (and O corrected)
+            tc_fence_after();
+            if (lane == 0) {
+                // O += Phi V + Plo V : P row = [hi 64 B | lo 64 B]; V tile MN-major, 32 keys per step
+#pragma unroll
+                for (int term = 0; term < 2; ++term)
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const uint64_t a = umma_desc(p_sm + term * 64 + k * 32, 16, 1024);
+                        const uint64_t b = umma_desc(vt + k * (32 * 128), PF_BN * 128, 1024);
+                        tc_mma_f8(tmem + PF_TMEM_O, a, b, IDESC_PV, (i | term | k) ? 1u : 0u);
+                    }
+                tc_commit(&kv_free[s]);
+                tc_commit(o_done);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ====================== softmax / correction / epilogue (warps 0-3) ======================
+        const int row = warp * 32 + lane;                                     // query row = TMEM lane
+        const bool row_ok = row < rows_here;
+        const long long qpos = p.pos + q0 + row;
+        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        // ---- stage the query block as two e4m3 copies (power-of-two row scale, hi + lo)
+        float qinv = 1.f;
+        {
+            const __nv_bfloat16 *qp = p.q + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D;
+            float amax = 0.f;
+            for (int c = 0; c < PF_D / 8; ++c) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(qp + c * 8);
+                const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(b2[e]); amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y))); }
+            }
+            int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;
+            if (amax == 0.f || e < -90 || !row_ok) e = 7;
+            if (e > 90) e = 90;
+            const float sc = row_ok ? __uint_as_float((uint32_t)(127 + 7 - e) << 23) : 0.f;
+            qinv = __uint_as_float((uint32_t)(127 - 7 + e) << 23);
+            for (int c = 0; c < PF_D / 16; ++c) {                              // 16 dims -> one 16-byte chunk of codes
+                uint32_t hw[4], lw[4];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const uint2 raw = *reinterpret_cast<const uint2 *>(qp + c * 16 + w * 4);
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+                    const float y[4] = {a.x * sc, a.y * sc, b.x * sc, b.y * sc};
+                    pf_split4(y, hw[w], lw[w]);
+                }
+                const uint32_t off = (c >> 3) * (PF_BM * 128) + sw128(row, (c & 7) * 16);
+                *reinterpret_cast<uint4 *>(smem + PF_OFF_Q + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                *reinterpret_cast<uint4 *>(smem + PF_OFF_Q + PF_Q_BYTES + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);                                     // phase 0: "Q staged"
+
+        float m_run = -INFINITY, l_run = 0.f;
+        const float qfac = qinv * p.scale_log2;
+        bool ok = true;
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int s = i % PF_STAGES;
+            const float *ksc = sm_sc + (s * 2 + 0) * PF_BN, *vsc = sm_sc + (s * 2 + 1) * PF_BN;
+            if (!(ok = mbar_wait(s_full, i & 1))) break;
+            tc_fence_after();
+            float sv[PF_BN];
+            {
+                float tmp[32];
+                tmem_ld32(lane_addr + PF_TMEM_S, tmp);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) sv[c] = tmp[c];
+                tmem_ld32(lane_addr + PF_TMEM_S + 32, tmp);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) sv[32 + c] = tmp[c];
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free);                                 // S may be overwritten by tile i+1
+            // scores -> exponent domain, mask, row maximum
+            const long long key0 = (long long)i * PF_BN;
+            float mt = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < PF_BN; ++c) {
+                const float tval = fmaf(sv[c], ksc[c] * qfac, __log2f(vsc[c]));
+                sv[c] = (key0 + c <= qpos && row_ok) ? tval : -INFINITY;
+                mt = fmaxf(mt, sv[c]);
+            }
+            const float m_new = fmaxf(m_run, mt);
+            const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run - m_safe);   // rows with no visible key yet
+            // the previous PV must have landed before P is overwritten or O is corrected
+            if (i > 0 && !(ok = mbar_wait(o_done, (i - 1) & 1))) break;
+            tc_fence_after();
+            if (__any_sync(0xffffffffu, alpha != 1.f) && i > 0) {
+#pragma unroll 1
+                for (int c = 0; c < PF_D / 32; ++c) {
+                    float ov[32];
+                    tmem_ld32(lane_addr + PF_TMEM_O + c * 32, ov);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) ov[e] *= alpha;
+                    tmem_st32(lane_addr + PF_TMEM_O + c * 32, ov);
+                }
+            }
+            float lsum = 0.f;
+#pragma unroll
+            for (int c = 0; c < PF_BN / 16; ++c) {                              // 16 keys -> one chunk of hi and of lo codes
+                uint32_t hw[4], lw[4];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    float y[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int kc = c * 16 + w * 4 + e;
+                        const float pv = fast_exp2(sv[kc] - m_safe);
+                        const float vsv = vsc[kc];
+                        lsum += (key0 + kc <= qpos && row_ok) ? __fdividef(pv, vsv) : 0.f;
+                        y[e] = pv * 256.f;
+                    }
+                    pf_split4(y, hw[w], lw[w]);
+                }
+                *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, c * 16)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, 64 + c * 16)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            }
+            l_run = fmaf(l_run, alpha, lsum);
+            m_run = m_new;
+            fence_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        // ---- epilogue: O / (256 * l) -> bf16
+        if (ok && n_tiles > 0) ok = mbar_wait(o_done, (n_tiles - 1) & 1);
+        tc_fence_after();
+        if (ok) {
+            const float inv = 1.f / (l_run * 256.f);
+            __nv_bfloat16 *op = p.out + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D;
+#pragma unroll 1
+            for (int c = 0; c < PF_D / 32; ++c) {
+                float ov[32];
+                tmem_ld32(lane_addr + PF_TMEM_O + c * 32, ov);
+                if (row_ok) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        uint4 o4;
+                        o4.x = pack_bf16x2(ov[e * 8 + 0] * inv, ov[e * 8 + 1] * inv);
+                        o4.y = pack_bf16x2(ov[e * 8 + 2] * inv, ov[e * 8 + 3] * inv);
+                        o4.z = pack_bf16x2(ov[e * 8 + 4] * inv, ov[e * 8 + 5] * inv);
+                        o4.w = pack_bf16x2(ov[e * 8 + 6] * inv, ov[e * 8 + 7] * inv);
+                        *reinterpret_cast<uint4 *>(op + c * 32 + e * 8) = o4;
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, PF_TMEM_COLS); }
+}
+
+}  // namespace trb
+
+using namespace trb;
 
 extern "C" int trb_attn_prefill(const trb_cache_t *cache, const void *q, void *out, int32_t t, int32_t hq, int64_t pos,
                                 float scale, trb_stream_t stream) {
-    (void)cache; (void)q; (void)out; (void)t; (void)hq; (void)pos; (void)scale; (void)stream;
-    return TRB_E_UNSUPPORTED;
+    CacheView c;
+    int rc = make_cache_view(cache, &c);
+    if (rc) return rc;
+    if (!q || !out || t < 1 || hq < 1 || hq % c.hkv || pos < 0) return TRB_E_ARG;
+    if (!c.fp8 || c.d != PF_D || c.ring > 0 || c.sharded) return TRB_E_UNSUPPORTED;
+    if (pos + t > c.max_len) return TRB_E_CAPACITY;
+    if (((uintptr_t)q | (uintptr_t)out) & 15) return TRB_E_ALIGN;
+    if (c.max_len >= (1LL << 31) - 64) return TRB_E_UNSUPPORTED;
+    PrefillParams p;
+    p.q = (const __nv_bfloat16 *)q; p.out = (__nv_bfloat16 *)out; p.ks = c.k_scale; p.vs = c.v_scale;
+    p.t = t; p.hq = hq; p.hkv = c.hkv; p.g = hq / c.hkv; p.pos = pos; p.max_len = c.max_len;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    CUtensorMap mk, mv;
+    if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, PF_D, PF_BN, &mk))) return rc;
+    if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, PF_D, PF_BN, &mv))) return rc;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    TRB_CUDA_CHECK(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+        TRB_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
+        attr_set[dev & 63] = true;
+    }
+    dim3 grid((t + PF_BM - 1) / PF_BM, hq);
+    prefill_kernel<<<grid, PF_THREADS, PF_SMEM, (cudaStream_t)stream>>>(mk, mv, p);
+    TRB_CUDA_CHECK(cudaGetLastError());
+    return TRB_OK;
 }
