@@ -17,6 +17,9 @@ Workloads (synthetic: N(0,1) values quantised into the FP8 cache layout, seeded)
     ctx32k       16 layers x 32768 rows
     ctx4k        16 layers x 4096 rows
     verify64k    M = 8 query rows over 65536 rows (speculative verify)
+    prefill8k    chunked prefill: 8192 new tokens over 131072 cached rows, 16 layers (metric:
+                 attention TFLOP/s against the dense bf16 peak; the chunk's K/V rows are appended to
+                 the FP8 cache in the same step)
 Inputs are far larger than L2 (126 MB), so consecutive steps cannot be served from cache.
 
 `--impl reference` times the CPU restatement of the reference's torch path (append + dequantise +
@@ -45,6 +48,7 @@ WORKLOADS = {
     "ctx32k": dict(ctx=32768, m=1),
     "ctx4k": dict(ctx=4096, m=1),
     "verify64k": dict(ctx=65536, m=8),
+    "prefill8k": dict(ctx=131072, t=8192),
 }
 # DRAM bytes per live row per layer-launch of the decode kernel from the ncu capture summarised in
 # profiles/decode_kernel_fp8_m1.md (dram__bytes_read.sum + dram__bytes_write.sum over 131072 rows)
@@ -296,6 +300,103 @@ def run_product(args):
         os._exit(0)
 
 
+def prefill_flops(t: int, pos: int) -> float:
+    """2 GEMMs x 2 flop/MAC over the causal region, all query heads, one layer."""
+    return 4.0 * HQ * D * (t * pos + t * (t + 1) / 2)
+
+
+def run_prefill(args):
+    """Chunked prefill (BASELINE config 4): per layer, append the chunk's K/V rows to the FP8 cache
+    and attend the chunk's queries causally over cache + chunk.  Single GPU."""
+    import tokenrush_b200 as tb
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    wl = WORKLOADS[args.workload]
+    pos, t = wl["ctx"], wl["t"]
+    steps, warmup = max(1, min(args.steps, 10)), max(1, min(args.warmup, 3))
+    cfg = tb.AttnConfig(n_attn=LAYERS)
+    state = tb.State(cfg, pos + t + 64, "cuda", kv_dtype=torch.float8_e4m3fn)
+    fill_cache_(state, seed=0)
+    gen = torch.Generator().manual_seed(0)
+    h_q = torch.randn(t, HQ, D, generator=gen).to(torch.bfloat16).pin_memory()
+    h_k = torch.randn(HKV, t, D, generator=gen).to(torch.bfloat16).pin_memory()
+    h_v = torch.randn(HKV, t, D, generator=gen).to(torch.bfloat16).pin_memory()
+    h_out = torch.empty(t, HQ, D, dtype=torch.bfloat16).pin_memory()
+    d_q, d_k, d_v = h_q.cuda(), h_k.cuda(), h_v.cuda()
+    outs = [None] * LAYERS
+
+    def step():
+        for l in range(LAYERS):
+            tb.fused.kv_write_prefill(d_k, d_v, state, l, pos)
+            outs[l] = tb.fused.attn_prefill_fused(d_q, state.k[l], state.v[l], pos, cfg, state.k_scale[l], state.v_scale[l])
+
+    def timed(fn, n):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    for _ in range(warmup):
+        step()
+    with ClockSampler(torch.cuda.current_device()) as clocks:
+        ms = timed(step, steps)
+    flops = LAYERS * prefill_flops(t, pos)
+    value = flops * steps / (ms * 1e-3) / 1e12
+
+    def e2e_step():
+        for l in range(LAYERS):                                  # every layer's chunk comes from the host
+            d_q.copy_(h_q, non_blocking=True); d_k.copy_(h_k, non_blocking=True); d_v.copy_(h_v, non_blocking=True)
+            tb.fused.kv_write_prefill(d_k, d_v, state, l, pos)
+            o = tb.fused.attn_prefill_fused(d_q, state.k[l], state.v[l], pos, cfg, state.k_scale[l], state.v_scale[l])
+            h_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_steps = max(1, steps // 2)
+    ms_e2e = timed(e2e_step, e2e_steps)
+    e2e_value = flops * e2e_steps / (ms_e2e * 1e-3) / 1e12
+
+    def attn_only():
+        for l in range(LAYERS):
+            tb.fused.attn_prefill_fused(d_q, state.k[l], state.v[l], pos, cfg, state.k_scale[l], state.v_scale[l])
+    ms_k = timed(attn_only, 1)
+    peaks, how = measured_peaks()
+    peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
+    achieved = flops / (ms_k * 1e-3) / 1e12
+    # CPU sample: the oracle port on 32 query rows of one layer
+    import numpy as np
+    from oracle import kv_oracle as O
+    rows = np.linspace(0, t - 1, 32).astype(np.int64)
+    rng = np.random.default_rng(0)
+    kd = rng.standard_normal((HKV, pos + t, D), dtype=np.float32); vd = rng.standard_normal((HKV, pos + t, D), dtype=np.float32)
+    qf = rng.standard_normal((t, HQ, D), dtype=np.float32)
+    t0 = time.perf_counter()
+    O.attn_prefill(qf, kd, vd, pos, rows=rows)
+    dt = time.perf_counter() - t0
+    cpu_flops = float(sum(4.0 * HQ * D * (pos + r + 1) for r in rows))
+    line = {
+        "metric": "prefill_attn_tflops", "value": round(value, 1), "unit": "TFLOP/s", "ms_per_step": round(ms / steps, 3),
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8_e4m3 operands (q and p as hi+lo pairs), fp32 accumulate in TMEM", "data": "synthetic",
+        "config": {"workload": args.workload, "layers": LAYERS, "cached_rows": pos, "new_tokens": t, "heads": f"{HQ}q/{HKV}kv x {D}",
+                   "flop_per_step": flops, "l2": "inputs larger than L2 (no flush needed)"},
+        "e2e": {"value": round(e2e_value, 1), "unit": "TFLOP/s", "ms_per_step": round(ms_e2e / e2e_steps, 3),
+                "h2d_bytes_per_step": LAYERS * (h_q.numel() + h_k.numel() + h_v.numel()) * 2, "d2h_bytes_per_step": LAYERS * h_out.numel() * 2},
+        "gpu_launches": 2 * LAYERS * steps,
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "tensor", "kernel": "prefill_kernel", "achieved": round(achieved, 1), "peak": peak, "peak_source": how,
+                     "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None,
+                     "note": "algorithmic flops (each product counted once); the kernel issues two e4m3 MMAs per product at the FP8 rate"},
+        "cpu_baseline": {"value": round(cpu_flops / dt / 1e12, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"32 query rows of one layer over {pos + t} keys ({dt:.2f} s)"},
+        "device_status": tb._lib.device_status(),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_cpu_sample(ctx: int, m: int, budget_s: float = 15.0):
     """The oracle (a CPU port of the reference's torch path: append + dequantise + fp32 attention)
     on the host cores: layer-steps at the full context until the time budget is spent."""
@@ -331,6 +432,9 @@ def run_reference(args):
     if int(os.environ.get("RANK", "0")) != 0:
         return
     wl = WORKLOADS[args.workload]
+    if "t" in wl:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm covers the decode workloads; the prefill CPU sample is in the product line's cpu_baseline"}), flush=True)
+        return
     steps = max(1, min(args.steps, 8))
     base = run_cpu_sample(wl["ctx"], wl["m"], budget_s=min(60.0, 4.0 * steps))
     sec_step = base["seconds_per_layer_step"] * LAYERS
@@ -360,6 +464,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif "t" in WORKLOADS[args.workload]:
+        run_prefill(args)
     else:
         run_product(args)
 

@@ -40,7 +40,6 @@ constexpr int DEC_MIN_TILES = 4;                 // a split is not made smaller 
 constexpr int DEC_STAGE_BYTES_TOTAL = 192 * 1024;
 constexpr int DEC_MAX_SPLITS = 148;              // bounds the tail's weight table in shared memory
 constexpr int DEC_EPI_PAD = 4;                   // floats of padding per staged output row
-constexpr float DEC_P_SCALE = 256.f;             // probabilities are quantised as p * 256 (e4m3 hi + lo)
 
 struct DecodeParams {
     const __nv_bfloat16 *q;
@@ -97,25 +96,6 @@ template <bool FP8>
 __device__ __forceinline__ int acc_dim(int a, int i, int g) {
     if (FP8) return 32 * (a >> 1) + 16 * (i >> 1) + 2 * g + (a & 1);
     return 16 * a + 8 * (i >> 1) + g;
-}
-
-// D = A(16x32 e4m3, row) * B(32x8 e4m3, col) + C, fp32 accumulate (full precision on sm_100).
-__device__ __forceinline__ void mma_e4m3(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// x (fp32) -> two e4m3 codes with x ~= hi + lo; four values -> one word of hi codes, one of lo codes
-__device__ __forceinline__ void split_e4m3x4(const float (&x)[4], uint32_t &hi, uint32_t &lo) {
-    const __nv_fp8x2_storage_t h01 = __nv_cvt_float2_to_fp8x2(make_float2(x[0], x[1]), __NV_SATFINITE, __NV_E4M3);
-    const __nv_fp8x2_storage_t h23 = __nv_cvt_float2_to_fp8x2(make_float2(x[2], x[3]), __NV_SATFINITE, __NV_E4M3);
-    const float2 f01 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(h01, __NV_E4M3)));
-    const float2 f23 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(h23, __NV_E4M3)));
-    const __nv_fp8x2_storage_t l01 = __nv_cvt_float2_to_fp8x2(make_float2(x[0] - f01.x, x[1] - f01.y), __NV_SATFINITE, __NV_E4M3);
-    const __nv_fp8x2_storage_t l23 = __nv_cvt_float2_to_fp8x2(make_float2(x[2] - f23.x, x[3] - f23.y), __NV_SATFINITE, __NV_E4M3);
-    hi = (uint32_t)h01 | ((uint32_t)h23 << 16);
-    lo = (uint32_t)l01 | ((uint32_t)l23 << 16);
 }
 
 template <int D, bool FP8>
@@ -203,10 +183,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
     };
     const bool issuer = warp_on && nt_idx == 0;
-#ifndef TRB_DEC_NOLOAD
     if (issuer)
         for (int i = kw_idx; i < my_tiles && i < C::NSTAGE; i += p.kw) issue_tile(i);
-#endif
 
     // ---- query fragments (the B operand of S^T = K Q^T) into shared memory, once per CTA:
     // warp w < nt prepares slice w; lane (g, t) owns column n = g (row 8w + g) and the dims
@@ -294,15 +272,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll 1
         for (int i = kw_idx; i < my_tiles; i += p.kw) {
             const int s = i % C::NSTAGE;
-#ifndef TRB_DEC_NOLOAD
             if (!mbar_wait(&bar_full[s], (i / C::NSTAGE) & 1)) break;
-#endif
             const int key0 = (t0 + i) * DEC_BN;                                    // virtual row of the tile
-#ifdef TRB_DEC_NOCOMPUTE
-            if (false) {
-#else
             if (key0 < lloc_i && key0 + DEC_BN - 1 >= row_lo_i) {
-#endif
                 const uint32_t kt = smem_u32(smem + s * 2 * C::TILE);
                 const uint32_t vt = kt + C::TILE;
                 const float *scl = sm_scale + s * 2 * DEC_BN;
@@ -457,12 +429,10 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_empty[s]);
-#ifndef TRB_DEC_NOLOAD
             if (issuer && i + C::NSTAGE < my_tiles) {          // refill the stage once every slice has left it
                 if (!mbar_wait(&bar_empty[s], (i / C::NSTAGE) & 1)) break;
                 issue_tile(i + C::NSTAGE);
             }
-#endif
         }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
