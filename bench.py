@@ -51,8 +51,8 @@ WORKLOADS = {
     "prefill8k": dict(ctx=131072, t=8192),
 }
 # DRAM bytes per live row per layer-launch of the decode kernel from the ncu capture summarised in
-# profiles/decode_kernel_fp8_m1.md (dram__bytes_read.sum + dram__bytes_write.sum over 131072 rows)
-NCU_TRAFFIC_BYTES_PER_ROW = None
+# profiles/decode_kernel_fp8_m1_window256k.md (dram__bytes_read.sum + dram__bytes_write.sum over 131072 rows)
+NCU_TRAFFIC_BYTES_PER_ROW = 2111
 
 
 def measured_peaks():
