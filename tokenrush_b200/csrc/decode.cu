@@ -98,7 +98,7 @@ __device__ __forceinline__ int acc_dim(int a, int i, int g) {
     return 16 * a + 8 * (i >> 1) + g;
 }
 
-template <int D, bool FP8>
+template <int D, bool FP8, int GS>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
     using C = DecodeCfg<D, FP8>;
@@ -143,7 +143,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::NSTAGE; ++s) {
             mbar_init(&bar_full[s], FP8 ? 33u : 1u);
-            mbar_init(&bar_empty[s], (uint32_t)p.nt);
+            mbar_init(&bar_empty[s], (uint32_t)(p.nt * (2 / GS)));
         }
         mbar_fence_init();
         tma_prefetch_desc(&tm_k);
@@ -154,9 +154,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     // =============================== consumer warps ======================================
     const int g = lane >> 2, t = lane & 3;
 
-    const bool warp_on = warp < p.nt * p.kw;
+    // warp -> (slice, 16-key group of a tile when a tile is shared by two warps, tile stream)
+    constexpr int GPT = 2 / GS;                                // warps per tile and slice
+    const bool warp_on = warp < p.nt * p.kw * GPT;
     const int nt_idx = warp_on ? warp % p.nt : 0;
-    const int kw_idx = warp_on ? warp / p.nt : 0;
+    const int grp_idx = warp_on ? (warp / p.nt) % GPT : 0;
+    const int kw_idx = warp_on ? warp / (p.nt * GPT) : 0;
+    const int gb = grp_idx * 16;                               // first key row of this warp's group(s) in a tile
     const unsigned int epoch = threadIdx.x == 0 ? *(volatile unsigned int *)&p.counters[128 + j] : 0u;
 
     // Loads of tile i into stage i % NSTAGE: issued by the slice-0 warp of the group that owns
@@ -182,7 +186,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             cp_async_mbar_arrive_noinc(&bar_full[s]);
         }
     };
-    const bool issuer = warp_on && nt_idx == 0;
+    const bool issuer = warp_on && nt_idx == 0 && grp_idx == 0;
     if (issuer)
         for (int i = kw_idx; i < my_tiles && i < C::NSTAGE; i += p.kw) issue_tile(i);
 
@@ -274,66 +278,67 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             const int s = i % C::NSTAGE;
             if (!mbar_wait(&bar_full[s], (i / C::NSTAGE) & 1)) break;
             const int key0 = (t0 + i) * DEC_BN;                                    // virtual row of the tile
-            if (key0 < lloc_i && key0 + DEC_BN - 1 >= row_lo_i) {
+            if (key0 + gb < lloc_i && key0 + gb + 16 * GS - 1 >= row_lo_i) {
                 const uint32_t kt = smem_u32(smem + s * 2 * C::TILE);
                 const uint32_t vt = kt + C::TILE;
                 const float *scl = sm_scale + s * 2 * DEC_BN;
-                // ---- S^T[32 keys, 8 columns] = K Q^T: two 16-key groups, two chains each
-                float sc4[2][2][4];
+                // ---- S^T[16 GS keys, 8 columns] = K Q^T per 16-key group, two accumulation chains each
+                float sc4[GS][2][4];
 #pragma unroll
-                for (int a = 0; a < 2; ++a)
+                for (int a = 0; a < GS; ++a)
 #pragma unroll
                     for (int b = 0; b < 2; ++b)
 #pragma unroll
                         for (int e = 0; e < 4; ++e) sc4[a][b][e] = 0.f;
 #pragma unroll
                 for (int q = 0; q < NQ; ++q) {
-                    const uint32_t ka = kt + k_lane + (((2u * q + k_chunk) ^ urr) << 4);
+                    const uint32_t ka = kt + k_lane + gb * 128 + (((2u * q + k_chunk) ^ urr) << 4);
 #pragma unroll
                     for (int sg = 0; sg < NSEG; ++sg) {
                         const int cp = 4 * sg + q;
-                        uint32_t r0[4], r1[4];
-                        ldmatrix_x4(r0, ka + sg * (DEC_BN * 128));
-                        ldmatrix_x4(r1, ka + sg * (DEC_BN * 128) + 16 * 128);
+                        uint32_t qw[4];
                         if (FP8) {
-                            // e4m3 -> f16 in registers (exact); low half-words feed one MMA, high ones the next
                             const uint4 qv = *reinterpret_cast<const uint4 *>(qf + cp * 32 * 4);
-                            uint32_t af[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r0[e] & 0xffffu));
-                            mma_f16(sc4[0][0], af, qv.x, qv.y);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r0[e] >> 16));
-                            mma_f16(sc4[0][1], af, qv.z, qv.w);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r1[e] & 0xffffu));
-                            mma_f16(sc4[1][0], af, qv.x, qv.y);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r1[e] >> 16));
-                            mma_f16(sc4[1][1], af, qv.z, qv.w);
+                            qw[0] = qv.x; qw[1] = qv.y; qw[2] = qv.z; qw[3] = qv.w;
                         } else {
                             const uint2 qv = *reinterpret_cast<const uint2 *>(qf + cp * 32 * 2);
-                            mma_bf16(sc4[0][sg & 1], r0, qv.x, qv.y);
-                            mma_bf16(sc4[1][sg & 1], r1, qv.x, qv.y);
+                            qw[0] = qv.x; qw[1] = qv.y; qw[2] = 0u; qw[3] = 0u;
+                        }
+#pragma unroll
+                        for (int a = 0; a < GS; ++a) {
+                            uint32_t r0[4];
+                            ldmatrix_x4(r0, ka + sg * (DEC_BN * 128) + a * (16 * 128));
+                            if (FP8) {
+                                // e4m3 -> f16 in registers (exact); low half-words feed one MMA, high ones the next
+                                uint32_t af[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r0[e] & 0xffffu));
+                                mma_f16(sc4[a][0], af, qw[0], qw[1]);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) af[e] = e4m3x2_to_f16x2((uint16_t)(r0[e] >> 16));
+                                mma_f16(sc4[a][1], af, qw[2], qw[3]);
+                            } else {
+                                mma_bf16(sc4[a][sg & 1], r0, qw[0], qw[1]);
+                            }
                         }
                     }
                 }
-                // tv[grp][e], e = 2*h + c -> key 16*grp + g + 8h, column 2t + c
-                float tv[2][4];
+                // tv[grp][e], e = 2*h + c -> key gb + 16*grp + g + 8h, column 2t + c
+                float tv[GS][4];
 #pragma unroll
-                for (int a = 0; a < 2; ++a)
+                for (int a = 0; a < GS; ++a)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) tv[a][e] = sc4[a][0][e] + sc4[a][1][e];
 
                 // ---- per-key factors: score scale, and the V scale moved into the exponent
-                float vr[2][2];
+                float vr[GS][2];
 #pragma unroll
-                for (int a = 0; a < 2; ++a)
+                for (int a = 0; a < GS; ++a)
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         if (FP8) {
-                            const float ksc = scl[a * 16 + g + 8 * h];
-                            const float vsc = scl[DEC_BN + a * 16 + g + 8 * h];
+                            const float ksc = scl[gb + a * 16 + g + 8 * h];
+                            const float vsc = scl[DEC_BN + gb + a * 16 + g + 8 * h];
                             const float vb = __log2f(vsc);
                             vr[a][h] = __fdividef(1.f, vsc);
                             tv[a][2 * h + 0] = fmaf(tv[a][2 * h + 0], ksc * qfac[0], vb);
@@ -355,20 +360,21 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                         if (p.new_rows && pos_loc + qi < hi) hi = pos_loc + qi;
                         const int lo = p.window > 0 ? pos_loc + qi - p.window + 1 : 0;
 #pragma unroll
-                        for (int a = 0; a < 2; ++a)
+                        for (int a = 0; a < GS; ++a)
 #pragma unroll
                             for (int h = 0; h < 2; ++h) {
-                                const int kv = key0 + a * 16 + g + 8 * h;
+                                const int kv = key0 + gb + a * 16 + g + 8 * h;
                                 if (!(kv <= hi && kv >= lo)) tv[a][2 * h + c] = -INFINITY;
                                 if (kv >= lloc_i) vr[a][h] = 0.f;            // never-written rows: scale may be anything
                             }
                     }
                 }
-                // ---- online softmax over the 32 keys (rows of S^T): reduce across the g lanes
+                // ---- online softmax over the keys (rows of S^T): reduce across the g lanes
                 float alpha[2];
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    float ml = fmaxf(fmaxf(tv[0][c], tv[0][2 + c]), fmaxf(tv[1][c], tv[1][2 + c]));
+                    float ml = fmaxf(tv[0][c], tv[0][2 + c]);
+                    if (GS == 2) ml = fmaxf(ml, fmaxf(tv[GS - 1][c], tv[GS - 1][2 + c]));
                     ml = fmaxf(ml, __shfl_xor_sync(0xffffffffu, ml, 4));
                     ml = fmaxf(ml, __shfl_xor_sync(0xffffffffu, ml, 8));
                     ml = fmaxf(ml, __shfl_xor_sync(0xffffffffu, ml, 16));
@@ -377,7 +383,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                     alpha[c] = fast_exp2(mx[c] - msafe);
                     float lsum = 0.f;
 #pragma unroll
-                    for (int a = 0; a < 2; ++a)
+                    for (int a = 0; a < GS; ++a)
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             const float pv = fast_exp2(tv[a][2 * h + c] - msafe);
@@ -397,12 +403,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 // ---- O^T[D dims, 8 columns] += V^T P^T per 16-key group; P^T as the B operand: pack the
                 // two columns of a key, transpose the 8x8 blocks across the warp
 #pragma unroll
-                for (int a = 0; a < 2; ++a) {
+                for (int a = 0; a < GS; ++a) {
                     const uint32_t pb0 = movmatrix_trans(FP8 ? pack_f16x2(tv[a][0], tv[a][1]) : pack_bf16x2(tv[a][0], tv[a][1]));
                     const uint32_t pb1 = movmatrix_trans(FP8 ? pack_f16x2(tv[a][2], tv[a][3]) : pack_bf16x2(tv[a][2], tv[a][3]));
 #pragma unroll
                     for (int q = 0; q < NQ; ++q) {
-                        const uint32_t va = vt + v_lane + (((2u * q + v_chunk) ^ urr) << 4) + a * (16 * 128);
+                        const uint32_t va = vt + v_lane + (((2u * q + v_chunk) ^ urr) << 4) + (gb + a * 16) * 128;
 #pragma unroll
                         for (int sg = 0; sg < NSEG; ++sg) {
                             const int cp = 4 * sg + q;
@@ -457,7 +463,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
             float mg = -INFINITY;
-            for (int k = 0; k < p.kw; ++k) mg = fmaxf(mg, sm_ml[((k * p.nt + nt_idx) * 8 + 2 * t + c) * 2]);
+            for (int k = 0; k < p.kw * GPT; ++k) mg = fmaxf(mg, sm_ml[((k * p.nt + nt_idx) * 8 + 2 * t + c) * 2]);
             wgt[c] = mg == -INFINITY ? 0.f : fast_exp2(mx[c] - mg);
         }
 #pragma unroll
@@ -474,7 +480,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (row >= p.rows) continue;
         const int nti = row >> 3, qc = row & 7;
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int k = 0; k < p.kw; ++k) {
+        for (int k = 0; k < p.kw * GPT; ++k) {
             const float4 v = *reinterpret_cast<const float4 *>(&stage_acc[((k * p.nt + nti) * 8 + qc) * SROW + d4]);
             sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
         }
@@ -483,9 +489,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     for (int row = tid; row < p.rows; row += DEC_CTHREADS) {
         const int nti = row >> 3, qc = row & 7;
         float mg = -INFINITY;
-        for (int k = 0; k < p.kw; ++k) mg = fmaxf(mg, sm_ml[((k * p.nt + nti) * 8 + qc) * 2]);
+        for (int k = 0; k < p.kw * GPT; ++k) mg = fmaxf(mg, sm_ml[((k * p.nt + nti) * 8 + qc) * 2]);
         float lg = 0.f;
-        for (int k = 0; k < p.kw; ++k) {
+        for (int k = 0; k < p.kw * GPT; ++k) {
             const float mk = sm_ml[((k * p.nt + nti) * 8 + qc) * 2], lk = sm_ml[((k * p.nt + nti) * 8 + qc) * 2 + 1];
             lg += mk == -INFINITY ? 0.f : lk * fast_exp2(mk - mg);
         }
@@ -702,20 +708,30 @@ static WorkspaceLayout workspace_layout(int hkv, int nsplit, int rows_pad, int d
     return w;
 }
 
-template <int D, bool FP8>
-static int launch_decode(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, cudaStream_t st) {
+template <int D, bool FP8, int GS>
+static int launch_decode_gs(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, cudaStream_t st) {
     using C = DecodeCfg<D, FP8>;
     static bool attr_set[64] = {};
     int dev = 0;
     TRB_CUDA_CHECK(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        TRB_CUDA_CHECK(cudaFuncSetAttribute(decode_kernel<D, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        TRB_CUDA_CHECK(cudaFuncSetAttribute(decode_kernel<D, FP8, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         attr_set[dev & 63] = true;
     }
     dim3 grid(p.nsplit, p.hkv);
-    decode_kernel<D, FP8><<<grid, DEC_THREADS, C::SMEM, st>>>(mk, mv, p);
+    decode_kernel<D, FP8, GS><<<grid, DEC_THREADS, C::SMEM, st>>>(mk, mv, p);
     TRB_CUDA_CHECK(cudaGetLastError());
     return TRB_OK;
+}
+
+// One slice (M = 1, the bandwidth-bound case): two warps share a tile, one 16-key group each, so
+// that half of the stage ring is always in flight.  More slices are bound by instruction issue
+// and the tensor pipe; there a warp takes whole 32-key tiles (one softmax step per 32 keys).
+static int decode_groups_per_warp(int nt) { return nt == 1 ? 1 : 2; }
+
+template <int D, bool FP8>
+static int launch_decode(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, cudaStream_t st) {
+    return decode_groups_per_warp(p.nt) == 2 ? launch_decode_gs<D, FP8, 2>(mk, mv, p, st) : launch_decode_gs<D, FP8, 1>(mk, mv, p, st);
 }
 
 }  // namespace trb
@@ -756,7 +772,7 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     p.gate_rs = a->gate_row_stride; p.gate_hs = a->gate_head_stride;
     p.ks = c.k_scale; p.vs = c.v_scale;
     p.m = a->m; p.hq = a->hq; p.hkv = c.hkv; p.g = g; p.rows = rows;
-    p.nt = (rows + 7) / 8; p.kw = DEC_CONSUMERS / p.nt;
+    p.nt = (rows + 7) / 8; p.kw = DEC_CONSUMERS / (p.nt * (2 / decode_groups_per_warp(p.nt)));
     p.nsplit = decode_nsplit(c.hkv); p.rows_pad = p.nt * 8;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.new_rows = a->new_rows ? 1 : 0; p.window = a->window; p.n_extra = a->n_extra;
