@@ -74,6 +74,12 @@ typedef struct trb_cursor {
 int         trb_version(void);
 const char *trb_strerror(int code);
 
+/* The append / prep / decode kernels are launched with programmatic stream serialization: each
+ * may start while its predecessor in the stream drains, and waits (griddepcontrol.wait) before
+ * it reads anything the predecessor may have written, so results do not change.  enable = 0
+ * switches to ordinary launches (also: environment variable TRB_PDL=0). */
+int trb_set_programmatic_launch(int enable);
+
 /* Read and clear the device status word of the current device.  Synchronises the device:
  * call it outside graph capture. */
 int trb_device_status(uint32_t *status_out);

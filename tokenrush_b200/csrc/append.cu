@@ -99,6 +99,8 @@ __global__ void __launch_bounds__(32) kv_append_kernel(CacheView c, const __nv_b
                                                        int has_valid) {
     constexpr int EPT = D / 32;
     const int i = blockIdx.x, head = blockIdx.y, which = blockIdx.z, lane = threadIdx.x;
+    pdl_launch_dependents();          // the decode that follows may start streaming old rows now
+    pdl_wait();                       // ... while this kernel waits for whatever produced its inputs
     if (has_valid && i >= load_cursor(n_valid)) return;
     const long long p = load_cursor(pos) + i;
     const long long row = row_of_position(c, p);
@@ -129,6 +131,8 @@ __global__ void __launch_bounds__(32) attn_prep_kernel(CacheView c, const __nv_b
     const int j = head - hq;
     const __nv_bfloat16 *src = qkv + i * qkv_w + (is_q ? (long long)head * 2 * D : (long long)hq * 2 * D + (long long)j * D);
     const __nv_bfloat16 *w = is_q ? qw : kw;
+    pdl_launch_dependents();
+    pdl_wait();
     const long long p = load_cursor(pos) + i;
 
     float x[EPT];
@@ -241,13 +245,10 @@ extern "C" int trb_kv_append(const trb_cache_t *cache, const void *k_src, const 
     dim3 grid(n_rows, c.hkv, 2);
     Cursor pc = make_cursor(pos), nv = make_cursor(n_valid);
     cudaStream_t st = (cudaStream_t)stream;
-    if (c.d == 256)
-        kv_append_kernel<256><<<grid, 32, 0, st>>>(c, (const __nv_bfloat16 *)k_src, (const __nv_bfloat16 *)v_src,
-                                                   src_head_stride, src_row_stride, pc, nv, n_valid != nullptr);
-    else
-        kv_append_kernel<128><<<grid, 32, 0, st>>>(c, (const __nv_bfloat16 *)k_src, (const __nv_bfloat16 *)v_src,
-                                                   src_head_stride, src_row_stride, pc, nv, n_valid != nullptr);
-    TRB_CUDA_CHECK(cudaGetLastError());
+    const int hv = n_valid != nullptr;
+    TRB_CUDA_CHECK(launch_kernel(c.d == 256 ? kv_append_kernel<256> : kv_append_kernel<128>, grid, dim3(32), 0, st, true, c,
+                                 (const __nv_bfloat16 *)k_src, (const __nv_bfloat16 *)v_src, (long long)src_head_stride,
+                                 (long long)src_row_stride, pc, nv, hv));
     return TRB_OK;
 }
 
@@ -265,17 +266,10 @@ extern "C" int trb_attn_prep(const trb_cache_t *cache, const void *qkv, const vo
     dim3 grid(hq + c.hkv, m);
     Cursor pc = make_cursor(pos);
     cudaStream_t st = (cudaStream_t)stream;
-    if (c.d == 256)
-        attn_prep_kernel<256><<<grid, 32, 0, st>>>(c, (const __nv_bfloat16 *)qkv, (const __nv_bfloat16 *)q_norm_w,
-                                                   (const __nv_bfloat16 *)k_norm_w, (const __nv_bfloat16 *)cos,
-                                                   (const __nv_bfloat16 *)sin, table_rows, rotary_dim, eps, hq, pc,
-                                                   (__nv_bfloat16 *)q_out);
-    else
-        attn_prep_kernel<128><<<grid, 32, 0, st>>>(c, (const __nv_bfloat16 *)qkv, (const __nv_bfloat16 *)q_norm_w,
-                                                   (const __nv_bfloat16 *)k_norm_w, (const __nv_bfloat16 *)cos,
-                                                   (const __nv_bfloat16 *)sin, table_rows, rotary_dim, eps, hq, pc,
-                                                   (__nv_bfloat16 *)q_out);
-    TRB_CUDA_CHECK(cudaGetLastError());
+    TRB_CUDA_CHECK(launch_kernel(c.d == 256 ? attn_prep_kernel<256> : attn_prep_kernel<128>, grid, dim3(32), 0, st, true, c,
+                                 (const __nv_bfloat16 *)qkv, (const __nv_bfloat16 *)q_norm_w, (const __nv_bfloat16 *)k_norm_w,
+                                 (const __nv_bfloat16 *)cos, (const __nv_bfloat16 *)sin, (long long)table_rows, (int)rotary_dim, eps,
+                                 (int)hq, pc, (__nv_bfloat16 *)q_out));
     return TRB_OK;
 }
 

@@ -161,8 +161,6 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const int grp_idx = warp_on ? (warp / p.nt) % GPT : 0;
     const int kw_idx = warp_on ? warp / (p.nt * GPT) : 0;
     const int gb = grp_idx * 16;                               // first key row of this warp's group(s) in a tile
-    const unsigned int epoch = threadIdx.x == 0 ? *(volatile unsigned int *)&p.counters[128 + j] : 0u;
-
     // Loads of tile i into stage i % NSTAGE: issued by the slice-0 warp of the group that owns
     // the stage at that moment (TMA by lane 0, one scale pair per lane with cp.async).
     auto issue_tile = [&](int i) {
@@ -187,8 +185,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
     };
     const bool issuer = warp_on && nt_idx == 0 && grp_idx == 0;
+    // Rows written by the launch before this one (the append of this step) start at pos; tiles
+    // below them depend on nothing in flight, so their loads go out before the dependency wait and
+    // overlap the tail of the previous kernel in the stream.
+    const long long fresh_from = p.new_rows ? pos - p.shard_lo : (1LL << 62);
     if (issuer)
-        for (int i = kw_idx; i < my_tiles && i < C::NSTAGE; i += p.kw) issue_tile(i);
+        for (int i = kw_idx; i < my_tiles && i < C::NSTAGE; i += p.kw)
+            if ((long long)(t0 + i + 1) * DEC_BN <= fresh_from) issue_tile(i);
+    pdl_wait();                       // predecessor complete: its rows, q, and the workspace are ours
+    pdl_launch_dependents();
+    const unsigned int epoch = threadIdx.x == 0 ? *(volatile unsigned int *)&p.counters[128 + j] : 0u;
+    if (issuer)
+        for (int i = kw_idx; i < my_tiles && i < C::NSTAGE; i += p.kw)
+            if ((long long)(t0 + i + 1) * DEC_BN > fresh_from) issue_tile(i);
 
     // ---- query fragments (the B operand of S^T = K Q^T) into shared memory, once per CTA:
     // warp w < nt prepares slice w; lane (g, t) owns column n = g (row 8w + g) and the dims
@@ -719,8 +728,7 @@ static int launch_decode_gs(const CUtensorMap &mk, const CUtensorMap &mv, const 
         attr_set[dev & 63] = true;
     }
     dim3 grid(p.nsplit, p.hkv);
-    decode_kernel<D, FP8, GS><<<grid, DEC_THREADS, C::SMEM, st>>>(mk, mv, p);
-    TRB_CUDA_CHECK(cudaGetLastError());
+    TRB_CUDA_CHECK(launch_kernel(decode_kernel<D, FP8, GS>, grid, dim3(DEC_THREADS), (size_t)C::SMEM, st, true, mk, mv, p));
     return TRB_OK;
 }
 

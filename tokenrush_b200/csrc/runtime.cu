@@ -1,6 +1,7 @@
 // Library-wide host state: error strings, the device status word, and the cache of TMA
 // tensor maps (one per distinct cache view) used by the decode and prefill kernels.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -12,6 +13,22 @@ static thread_local char g_last_cuda[256] = "";
 
 void trb_set_last_cuda_error(cudaError_t e, const char *file, int line) {
     snprintf(g_last_cuda, sizeof(g_last_cuda), "%s (%s:%d)", cudaGetErrorString(e), file, line);
+}
+
+static int g_pdl = -1;
+namespace trb {
+bool pdl_enabled() {
+    if (g_pdl < 0) {
+        const char *e = getenv("TRB_PDL");
+        g_pdl = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_pdl != 0;
+}
+}  // namespace trb
+
+extern "C" int trb_set_programmatic_launch(int enable) {
+    g_pdl = enable ? 1 : 0;
+    return TRB_OK;
 }
 
 extern "C" int trb_version(void) { return 100; }
