@@ -174,7 +174,7 @@ def run_product(args):
         for l in range(LAYERS):
             if world > 1:
                 shard.sharded_decode_layer(state, l, d_q[l], d_k[l], d_v[l], cfg, xchg, out=d_out[l])
-                n += 3                                        # append, shard scan, exchange + merge
+                n += 2 if args.exchange == "fused" else 3      # append, shard scan (+ exchange and merge in its tail, or as a third launch)
             else:
                 tb.fused.kv_write_prefill(d_k[l], d_v[l], state, l, state.pos_t)
                 tb.fused.attn_decode_fused(d_q[l], None, state.k[l], state.v[l], state.pos_t, cfg, state.k_scale[l], state.v_scale[l],
@@ -459,7 +459,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="product", choices=["product", "reference"])
     ap.add_argument("--workload", default="window256k", choices=sorted(WORKLOADS))
-    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--exchange", default="fused", choices=["fused", "p2p", "nccl"])
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
     if args.impl == "reference":

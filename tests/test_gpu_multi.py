@@ -42,7 +42,7 @@ def _worker(rank, world, port, out_q):
             tb.fused.kv_append(dev(kb[:, lo:lo + n_old]), dev(vb[:, lo:lo + n_old]), st.k[1], st.v[1], lo, st.k_scale[1], st.v_scale[1],
                                shard_lo=st.shard_lo)
         results = {}
-        for mode in ("p2p", "nccl"):
+        for mode in ("fused", "p2p", "nccl"):
             xchg = shard.PartialExchange(HQ, D, HQ, mode=mode)
             st.set_pos(L)
             outs = []
@@ -86,9 +86,10 @@ def test_sharded_decode_over_nvlink(world):
     O.kv_write(ref, 0, 0, kb[:, :L], vb[:, :L])
     for t in range(steps):
         want = O.decode_step_cpu(ref, 0, qb[t:t + 1], kb[:, L + t:L + t + 1], vb[:, L + t:L + t + 1], L + t)
-        for mode in ("p2p", "nccl"):
+        for mode in ("fused", "p2p", "nccl"):
             got = results[mode][t].reshape(1, HQ, D)
             err = np.abs(got - want)
             rel = np.linalg.norm(got - want) / np.linalg.norm(want)
             assert (err <= 2e-3 + 2.0 ** -8 * np.abs(want)).all() and rel <= 1e-2, (mode, t, float(err.max()), float(rel))
     assert np.array_equal(results["p2p"], results["nccl"])      # same merge order, same bits
+    assert np.array_equal(results["fused"], results["nccl"])

@@ -39,7 +39,8 @@ class DecodeArgs(C.Structure):
                 ("new_rows", C.c_int32), ("window", C.c_int32), ("n_extra", C.c_int32),
                 ("extra_ml", C.c_void_p), ("extra_acc", C.c_void_p),
                 ("pos", Cursor), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-                ("partial_ml", C.c_void_p), ("partial_acc", C.c_void_p)]
+                ("partial_ml", C.c_void_p), ("partial_acc", C.c_void_p),
+                ("p2p_xchg", C.c_void_p), ("p2p_world", C.c_int32), ("p2p_rank", C.c_int32)]
 
 
 class P2PMergeArgs(C.Structure):

@@ -59,6 +59,8 @@ struct DecodeParams {
     unsigned int *counters;       // [3][64]: tickets, slice claims, launch epochs (per kv head)
     float *part_ml, *part_acc;
     float *shard_ml, *shard_acc;
+    void *const *p2p_xchg;        // sequence shards: every GPU's exchange buffer as mapped here
+    int p2p_world, p2p_rank;
 };
 
 template <int D, bool FP8>
@@ -525,12 +527,15 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             *(volatile unsigned int *)seq = epoch + 1u;
         } else {
             state = 0;
-            for (int it = 0; it < 4096; ++it) {
+            // only the last `rows` arrivals can find a row to merge; earlier ones leave at once and
+            // free their SM for the next kernel in the stream
+            for (int it = 0; it < 4096 && (int)old >= active - p.rows; ++it) {
                 if (*(volatile unsigned int *)seq == epoch + 1u) { state = 1; break; }
                 __nanosleep(100);
             }
         }
         *sm_flag = state;
+        sm_flag[2] = (int)epoch;
     }
     __syncthreads();
     if (*sm_flag == 0) return;                                          // gave up waiting: the others finish the rows
@@ -583,16 +588,68 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
         sm_red[grp * ITEMS + item] = o;
         __syncthreads();
-        if (grp != 0) continue;
-        for (int k = 1; k < GROUPS; ++k) {
-            const float4 v = sm_red[k * ITEMS + item];
-            o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
+        const bool lead = grp == 0;                                      // these threads hold the row from here on
+        if (lead) {
+            for (int k = 1; k < GROUPS; ++k) {
+                const float4 v = sm_red[k * ITEMS + item];
+                o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
+            }
         }
         if (p.shard_acc) {
-            *reinterpret_cast<float4 *>(&p.shard_acc[grow * D + d4]) = o;
-            if (item == 0) { p.shard_ml[grow * 2] = mmax; p.shard_ml[grow * 2 + 1] = lsum; }
+            if (lead) {
+                *reinterpret_cast<float4 *>(&p.shard_acc[grow * D + d4]) = o;
+                if (item == 0) { p.shard_ml[grow * 2] = mmax; p.shard_ml[grow * 2 + 1] = lsum; }
+            }
             continue;
         }
+        if (p.p2p_world > 1) {
+            // ---- sequence shards: exchange this row's (max, sum, acc) with the other GPUs by peer
+            // stores, wait (bounded) for theirs, merge in rank order.  The tag is this kv head's launch
+            // epoch, identical on all GPUs because they make the same calls on their workspaces.
+            const P2PLayout xl = p2p_layout(p.p2p_world, p.m * p.hq, D);
+            const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
+            const size_t slot = tag % P2P_SLOTS;
+            if (lead) {
+                for (int r = 0; r < p.p2p_world; ++r) {
+                    float *dst = (float *)((uint8_t *)p.p2p_xchg[r] + xl.data) + ((slot * p.p2p_world + p.p2p_rank) * (size_t)(p.m * p.hq) + grow) * xl.row_floats;
+                    *reinterpret_cast<float4 *>(dst + d4) = o;
+                    if (item == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(mmax, lsum);
+                }
+            }
+            __threadfence_system();
+            __syncthreads();
+            uint8_t *local = (uint8_t *)p.p2p_xchg[p.p2p_rank];
+            if (tid < p.p2p_world) {
+                unsigned int *flag = (unsigned int *)((uint8_t *)p.p2p_xchg[tid] + xl.flags) + (slot * p.p2p_world + p.p2p_rank) * (size_t)(p.m * p.hq) + grow;
+                st_release_sys(flag, tag);
+                const unsigned int *mine = (const unsigned int *)(local + xl.flags) + (slot * p.p2p_world + tid) * (size_t)(p.m * p.hq) + grow;
+                bool ok = false;
+                for (unsigned int it = 0; it < P2P_SPIN_LIMIT; ++it) {
+                    if (ld_acquire_sys(mine) == tag) { ok = true; break; }
+                    if (it > 32) __nanosleep(200);
+                }
+                if (!ok) raise_status(TRB_ST_PEER_TIMEOUT);
+            }
+            __syncthreads();
+            if (lead) {
+                const float *data = (const float *)(local + xl.data);
+                float gm = -INFINITY;
+                for (int r = 0; r < p.p2p_world; ++r)
+                    gm = fmaxf(gm, __ldcg(data + ((slot * p.p2p_world + r) * (size_t)(p.m * p.hq) + grow) * xl.row_floats + D));
+                float gl = 0.f;
+                float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int r = 0; r < p.p2p_world; ++r) {
+                    const float *src = data + ((slot * p.p2p_world + r) * (size_t)(p.m * p.hq) + grow) * xl.row_floats;
+                    const float2 mlr = __ldcg(reinterpret_cast<const float2 *>(src + D));
+                    const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
+                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + d4));
+                    gl = fmaf(w, mlr.y, gl);
+                    go.x = fmaf(w, v.x, go.x); go.y = fmaf(w, v.y, go.y); go.z = fmaf(w, v.z, go.z); go.w = fmaf(w, v.w, go.w);
+                }
+                o = go; lsum = gl;
+            }
+        }
+        if (!lead) continue;
         const float inv = 1.f / lsum;
         float r[4] = {o.x * inv, o.y * inv, o.z * inv, o.w * inv};
         __nv_bfloat16 ob[4];
@@ -793,6 +850,8 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     p.counters = (unsigned int *)(ws + w.counters);
     p.part_ml = (float *)(ws + w.ml); p.part_acc = (float *)(ws + w.acc);
     p.shard_ml = a->partial_ml; p.shard_acc = a->partial_acc;
+    p.p2p_xchg = a->p2p_xchg; p.p2p_world = a->p2p_xchg ? a->p2p_world : 1; p.p2p_rank = a->p2p_rank;
+    if (p.p2p_world > 1 && (p.p2p_world > P2P_MAX_WORLD || p.p2p_rank < 0 || p.p2p_rank >= p.p2p_world || a->partial_acc)) return TRB_E_ARG;
 
     const int row_bytes = c.d * (c.fp8 ? 1 : 2);
     CUtensorMap mk, mv;

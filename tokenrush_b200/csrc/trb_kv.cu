@@ -4,6 +4,6 @@
 
 #include "runtime.cu"
 #include "append.cu"
-#include "decode.cu"
 #include "p2p.cu"
+#include "decode.cu"
 #include "prefill.cu"

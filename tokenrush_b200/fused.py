@@ -132,7 +132,7 @@ def attn_prep(qkv, q_norm_w, k_norm_w, cos, sin, pos_t, k_cache, v_cache, cfg, k
 # ------------------------------------------------------------------------------ decode
 
 def _decode(q, k_cache, v_cache, pos, HQ, HKV, D, k_scale, v_scale, *, gate=None, gate_rs=0, gate_hs=0, new_rows=1,
-            window=0, ring=0, shard_lo=None, extra=None, partial=False, scale=None, out=None):
+            window=0, ring=0, shard_lo=None, extra=None, partial=False, scale=None, out=None, p2p=None):
     _need_cuda(q)
     if q.dtype != torch.bfloat16 or not q.is_contiguous():
         raise ValueError("q must be contiguous bf16 [M, HQ*D]")
@@ -150,6 +150,8 @@ def _decode(q, k_cache, v_cache, pos, HQ, HKV, D, k_scale, v_scale, *, gate=None
         a.gate, a.gate_row_stride, a.gate_head_stride = gate, gate_rs, gate_hs
     if extra is not None:
         a.n_extra, a.extra_ml, a.extra_acc = 1, extra[0].data_ptr(), extra[1].data_ptr()
+    if p2p is not None:                                   # (device array of exchange-buffer pointers, world, rank)
+        a.p2p_xchg, a.p2p_world, a.p2p_rank = p2p[0].data_ptr(), int(p2p[1]), int(p2p[2])
     if partial:
         ml = torch.empty(M * HQ, 2, device=q.device, dtype=torch.float32)
         acc = torch.empty(M * HQ, D, device=q.device, dtype=torch.float32)
@@ -166,13 +168,15 @@ def _decode(q, k_cache, v_cache, pos, HQ, HKV, D, k_scale, v_scale, *, gate=None
 
 
 def attn_decode_fused(q, qkv, k_cache, v_cache, pos_t, cfg, k_scale=None, v_scale=None, NSPLIT=32, BLOCK_N=32,
-                      shard_lo=None, partial: bool = False, out=None):
+                      shard_lo=None, partial: bool = False, out=None, p2p=None):
     """q [M, HQ*D] (from attn_prep) for the M new tokens at pos.., qkv [M, ..] (for the gates;
     None: ungated) -> gated attention output [M, HQ*D]; query i sees cache rows <= pos + i.
     NSPLIT / BLOCK_N are accepted for signature compatibility; the split count is chosen
     from the SM count and the split ranges from the live length on the device.
     partial=True (sequence shards): returns this cache's (ml [M*HQ, 2], acc [M*HQ, D]).
-    out (optional): a preallocated [M, HQ*D] bf16 tensor to write instead of a new one."""
+    out (optional): a preallocated [M, HQ*D] bf16 tensor to write instead of a new one.
+    p2p (sequence shards, fused exchange): (device int64 tensor of the GPUs' exchange-buffer
+    pointers, world, rank); the kernel's tail then merges the partials of all GPUs itself."""
     HQ, HKV, D = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
     gate = None
     rs = hs = 0
@@ -180,7 +184,7 @@ def attn_decode_fused(q, qkv, k_cache, v_cache, pos_t, cfg, k_scale=None, v_scal
         _need_cuda(qkv)
         gate, rs, hs = qkv.data_ptr() + D * qkv.element_size(), qkv.stride(0), 2 * D
     return _decode(q, k_cache, v_cache, pos_t, HQ, HKV, D, k_scale, v_scale, gate=gate, gate_rs=rs, gate_hs=hs,
-                   new_rows=1, shard_lo=shard_lo, partial=partial, out=out)
+                   new_rows=1, shard_lo=shard_lo, partial=partial, out=out, p2p=p2p)
 
 
 def attn_window_block(q, k_cache, v_cache, pos_t, k_blk, v_blk, HQ, HKV, D, window, NSPLIT=15, BLOCK_N=32, ring=0):

@@ -5,11 +5,13 @@ The reference is single-GPU; its split kernel already reduces (max, sum, acc) tr
 reduction runs one level up: GPU g owns positions [g*S/G, (g+1)*S/G) of every layer's cache,
 scans its live rows, and the per-GPU partials are merged in rank order on every GPU.
 
-Two exchange paths:
-  * "p2p"  (default): plain peer stores over NVLink into exchange buffers shared with CUDA IPC
-    handles, one fused push + bounded wait + merge kernel per layer (trb_p2p_merge);
+Three exchange paths:
+  * "fused" (default): the decode kernel's tail pushes each row's partial into every GPU's
+    exchange buffer (plain peer stores over NVLink, buffers shared with CUDA IPC handles),
+    waits (bounded) for the peers' flags and merges: scan, exchange and merge are one launch;
+  * "p2p": the same exchange as a separate kernel after the scan (trb_p2p_merge);
   * "nccl": torch.distributed all_gather of the partials, then trb_lse_merge.  The baseline.
-Both produce the same bits: the merge order is the rank order.
+All produce the same bits: the merge order is the rank order.
 
 The appended row is written by the GPU that owns its position; every rank issues the same
 launches, the kernels skip positions they do not hold, so one captured graph is valid on
@@ -61,7 +63,7 @@ class ShardedState(State):
 class PartialExchange:
     """Exchange buffers for the per-layer merge of (max, sum, acc) partials of `rows` query rows."""
 
-    def __init__(self, rows: int, d: int, hq: int, group=None, mode: str = "p2p", device=None):
+    def __init__(self, rows: int, d: int, hq: int, group=None, mode: str = "fused", device=None):
         import torch.distributed as dist
         self.rows, self.d, self.hq, self.mode = rows, d, hq, mode
         self.group = group
@@ -70,7 +72,7 @@ class PartialExchange:
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self._local = None
         self._peers = []
-        if mode == "p2p":
+        if mode in ("p2p", "fused"):
             lib = L.lib()
             nbytes = lib.trb_p2p_exchange_bytes(self.world, rows, d)
             if nbytes == 0:
@@ -98,7 +100,7 @@ class PartialExchange:
             if self.world > 1:
                 dist.barrier(group=group)
         elif mode != "nccl":
-            raise ValueError("mode must be 'p2p' or 'nccl'")
+            raise ValueError("mode must be 'fused', 'p2p' or 'nccl'")
 
     def merge(self, ml: torch.Tensor, acc: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
         """ml [rows, 2], acc [rows, d] of this rank -> merged attention output [rows, d] bf16
@@ -125,7 +127,7 @@ class PartialExchange:
         return res
 
     def close(self):
-        if self.mode == "p2p" and self._local is not None:
+        if self.mode in ("p2p", "fused") and self._local is not None:
             torch.cuda.synchronize()
             lib = L.lib()
             for p in self._peers:
@@ -140,6 +142,9 @@ def sharded_decode_layer(state: ShardedState, slot: int, q, k_new, v_new, cfg, x
     ks = state.k_scale[slot] if state.fp8 else None
     vs = state.v_scale[slot] if state.fp8 else None
     fused.kv_append(k_new, v_new, state.k[slot], state.v[slot], state.pos_t, ks, vs, shard_lo=state.shard_lo)
+    if xchg.mode == "fused":
+        return fused.attn_decode_fused(q, None, state.k[slot], state.v[slot], state.pos_t, cfg, ks, vs, shard_lo=state.shard_lo,
+                                       out=out, p2p=(xchg.xchg, xchg.world, xchg.rank))
     ml, acc = fused.attn_decode_fused(q, None, state.k[slot], state.v[slot], state.pos_t, cfg, ks, vs,
                                       shard_lo=state.shard_lo, partial=True)
     res = xchg.merge(ml, acc, out=out)
