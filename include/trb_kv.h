@@ -137,7 +137,7 @@ typedef struct trb_decode_args {
     float      *partial_acc;     /* [m*hq, d]                                               */
     /* ... or, fused: when p2p_xchg is set (and p2p_world > 1) the tail exchanges the partials
      * with the other GPUs itself (peer stores + flags, bounded wait, rank-order merge) and
-     * writes the final out on every GPU.  p2p_xchg: DEVICE array of p2p_world pointers to the
+     * writes the final out on every GPU.  p2p_xchg: HOST array of p2p_world device pointers to the
      * GPUs' exchange buffers (trb_p2p_exchange_bytes(world, m*hq, d) bytes each, from
      * trb_p2p_create / trb_p2p_open).  All GPUs must make the same sequence of decode calls on
      * their workspaces: the launch count of the workspace tags the exchange.               */

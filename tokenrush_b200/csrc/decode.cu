@@ -59,8 +59,8 @@ struct DecodeParams {
     unsigned int *counters;       // [3][64]: tickets, slice claims, launch epochs (per kv head)
     float *part_ml, *part_acc;
     float *shard_ml, *shard_acc;
-    void *const *p2p_xchg;        // sequence shards: every GPU's exchange buffer as mapped here
-    int p2p_world, p2p_rank;
+    void *p2p_ptr[8];             // sequence shards: every GPU's exchange buffer as mapped here
+    int p2p_world, p2p_rank;      // p2p_world == 0: no exchange
 };
 
 template <int D, bool FP8>
@@ -602,47 +602,55 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
             continue;
         }
-        if (p.p2p_world > 1) {
+        if (p.p2p_world > 0) {
             // ---- sequence shards: exchange this row's (max, sum, acc) with the other GPUs by peer
             // stores, wait (bounded) for theirs, merge in rank order.  The tag is this kv head's launch
             // epoch, identical on all GPUs because they make the same calls on their workspaces.
+            // This GPU's own partial stays in registers; only the peers' go through memory.
             const P2PLayout xl = p2p_layout(p.p2p_world, p.m * p.hq, D);
             const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
             const size_t slot = tag % P2P_SLOTS;
+            const size_t nrow = (size_t)(p.m * p.hq);
             if (lead) {
                 for (int r = 0; r < p.p2p_world; ++r) {
-                    float *dst = (float *)((uint8_t *)p.p2p_xchg[r] + xl.data) + ((slot * p.p2p_world + p.p2p_rank) * (size_t)(p.m * p.hq) + grow) * xl.row_floats;
+                    if (r == p.p2p_rank) continue;
+                    float *dst = (float *)((uint8_t *)p.p2p_ptr[r] + xl.data) + ((slot * p.p2p_world + p.p2p_rank) * nrow + grow) * xl.row_floats;
                     *reinterpret_cast<float4 *>(dst + d4) = o;
                     if (item == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(mmax, lsum);
                 }
+                __threadfence_system();
             }
-            __threadfence_system();
             __syncthreads();
-            uint8_t *local = (uint8_t *)p.p2p_xchg[p.p2p_rank];
-            if (tid < p.p2p_world) {
-                unsigned int *flag = (unsigned int *)((uint8_t *)p.p2p_xchg[tid] + xl.flags) + (slot * p.p2p_world + p.p2p_rank) * (size_t)(p.m * p.hq) + grow;
-                st_release_sys(flag, tag);
-                const unsigned int *mine = (const unsigned int *)(local + xl.flags) + (slot * p.p2p_world + tid) * (size_t)(p.m * p.hq) + grow;
+            uint8_t *local = (uint8_t *)p.p2p_ptr[p.p2p_rank];
+            if (tid < p.p2p_world && tid != p.p2p_rank) {
+                volatile unsigned int *flag = (volatile unsigned int *)((uint8_t *)p.p2p_ptr[tid] + xl.flags) + (slot * p.p2p_world + p.p2p_rank) * nrow + grow;
+                *flag = tag;
+                const volatile unsigned int *mine = (const volatile unsigned int *)(local + xl.flags) + (slot * p.p2p_world + tid) * nrow + grow;
                 bool ok = false;
                 for (unsigned int it = 0; it < P2P_SPIN_LIMIT; ++it) {
-                    if (ld_acquire_sys(mine) == tag) { ok = true; break; }
-                    if (it > 32) __nanosleep(200);
+                    if (*mine == tag) { ok = true; break; }
+                    if (it > 64) __nanosleep(100);
                 }
                 if (!ok) raise_status(TRB_ST_PEER_TIMEOUT);
+                __threadfence_system();
             }
             __syncthreads();
-            if (lead) {
+            if (lead && p.p2p_world > 1) {
                 const float *data = (const float *)(local + xl.data);
-                float gm = -INFINITY;
+                float gm = mmax;
                 for (int r = 0; r < p.p2p_world; ++r)
-                    gm = fmaxf(gm, __ldcg(data + ((slot * p.p2p_world + r) * (size_t)(p.m * p.hq) + grow) * xl.row_floats + D));
+                    if (r != p.p2p_rank) gm = fmaxf(gm, __ldcg(data + ((slot * p.p2p_world + r) * nrow + grow) * xl.row_floats + D));
                 float gl = 0.f;
                 float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int r = 0; r < p.p2p_world; ++r) {
-                    const float *src = data + ((slot * p.p2p_world + r) * (size_t)(p.m * p.hq) + grow) * xl.row_floats;
-                    const float2 mlr = __ldcg(reinterpret_cast<const float2 *>(src + D));
+                for (int r = 0; r < p.p2p_world; ++r) {                  // rank order, own partial from registers
+                    float2 mlr = make_float2(mmax, lsum);
+                    float4 v = o;
+                    if (r != p.p2p_rank) {
+                        const float *src = data + ((slot * p.p2p_world + r) * nrow + grow) * xl.row_floats;
+                        mlr = __ldcg(reinterpret_cast<const float2 *>(src + D));
+                        v = __ldcg(reinterpret_cast<const float4 *>(src + d4));
+                    }
                     const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
-                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + d4));
                     gl = fmaf(w, mlr.y, gl);
                     go.x = fmaf(w, v.x, go.x); go.y = fmaf(w, v.y, go.y); go.z = fmaf(w, v.z, go.z); go.w = fmaf(w, v.w, go.w);
                 }
@@ -850,8 +858,16 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     p.counters = (unsigned int *)(ws + w.counters);
     p.part_ml = (float *)(ws + w.ml); p.part_acc = (float *)(ws + w.acc);
     p.shard_ml = a->partial_ml; p.shard_acc = a->partial_acc;
-    p.p2p_xchg = a->p2p_xchg; p.p2p_world = a->p2p_xchg ? a->p2p_world : 1; p.p2p_rank = a->p2p_rank;
-    if (p.p2p_world > 1 && (p.p2p_world > P2P_MAX_WORLD || p.p2p_rank < 0 || p.p2p_rank >= p.p2p_world || a->partial_acc)) return TRB_E_ARG;
+    p.p2p_world = 0; p.p2p_rank = 0;
+    for (int r = 0; r < 8; ++r) p.p2p_ptr[r] = nullptr;
+    if (a->p2p_xchg) {
+        if (a->p2p_world < 1 || a->p2p_world > P2P_MAX_WORLD || a->p2p_rank < 0 || a->p2p_rank >= a->p2p_world || a->partial_acc) return TRB_E_ARG;
+        p.p2p_world = a->p2p_world; p.p2p_rank = a->p2p_rank;
+        for (int r = 0; r < a->p2p_world; ++r) {
+            if (!a->p2p_xchg[r]) return TRB_E_ARG;
+            p.p2p_ptr[r] = a->p2p_xchg[r];
+        }
+    }
 
     const int row_bytes = c.d * (c.fp8 ? 1 : 2);
     CUtensorMap mk, mv;

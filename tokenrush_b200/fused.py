@@ -150,8 +150,8 @@ def _decode(q, k_cache, v_cache, pos, HQ, HKV, D, k_scale, v_scale, *, gate=None
         a.gate, a.gate_row_stride, a.gate_head_stride = gate, gate_rs, gate_hs
     if extra is not None:
         a.n_extra, a.extra_ml, a.extra_acc = 1, extra[0].data_ptr(), extra[1].data_ptr()
-    if p2p is not None:                                   # (device array of exchange-buffer pointers, world, rank)
-        a.p2p_xchg, a.p2p_world, a.p2p_rank = p2p[0].data_ptr(), int(p2p[1]), int(p2p[2])
+    if p2p is not None:                                   # (host ctypes array of exchange-buffer pointers, world, rank)
+        a.p2p_xchg, a.p2p_world, a.p2p_rank = C.cast(p2p[0], C.c_void_p), int(p2p[1]), int(p2p[2])
     if partial:
         ml = torch.empty(M * HQ, 2, device=q.device, dtype=torch.float32)
         acc = torch.empty(M * HQ, D, device=q.device, dtype=torch.float32)
@@ -175,7 +175,7 @@ def attn_decode_fused(q, qkv, k_cache, v_cache, pos_t, cfg, k_scale=None, v_scal
     from the SM count and the split ranges from the live length on the device.
     partial=True (sequence shards): returns this cache's (ml [M*HQ, 2], acc [M*HQ, D]).
     out (optional): a preallocated [M, HQ*D] bf16 tensor to write instead of a new one.
-    p2p (sequence shards, fused exchange): (device int64 tensor of the GPUs' exchange-buffer
+    p2p (sequence shards, fused exchange): (ctypes array of the GPUs' exchange-buffer
     pointers, world, rank); the kernel's tail then merges the partials of all GPUs itself."""
     HQ, HKV, D = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
     gate = None

@@ -95,7 +95,8 @@ class PartialExchange:
                     L.check(lib.trb_p2p_open(handles[r], C.byref(peer)), "trb_p2p_open")
                     self._peers.append(peer.value)
                     ptrs.append(peer.value)
-            self.xchg = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
+            self.xchg = torch.tensor(ptrs, dtype=torch.int64, device=self.device)     # device array (separate merge kernel)
+            self.xchg_host = (C.c_void_p * self.world)(*ptrs)                            # host array (fused tail)
             self.seq = torch.zeros(1, dtype=torch.int32, device=self.device)
             if self.world > 1:
                 dist.barrier(group=group)
@@ -144,7 +145,7 @@ def sharded_decode_layer(state: ShardedState, slot: int, q, k_new, v_new, cfg, x
     fused.kv_append(k_new, v_new, state.k[slot], state.v[slot], state.pos_t, ks, vs, shard_lo=state.shard_lo)
     if xchg.mode == "fused":
         return fused.attn_decode_fused(q, None, state.k[slot], state.v[slot], state.pos_t, cfg, ks, vs, shard_lo=state.shard_lo,
-                                       out=out, p2p=(xchg.xchg, xchg.world, xchg.rank))
+                                       out=out, p2p=(xchg.xchg_host, xchg.world, xchg.rank))
     ml, acc = fused.attn_decode_fused(q, None, state.k[slot], state.v[slot], state.pos_t, cfg, ks, vs,
                                       shard_lo=state.shard_lo, partial=True)
     res = xchg.merge(ml, acc, out=out)
