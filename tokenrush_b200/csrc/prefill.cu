@@ -31,7 +31,8 @@ constexpr int PF_OFF_Q = 0;                            // Qhi, Qlo
 constexpr int PF_OFF_KV = 2 * PF_Q_BYTES;              // stages of (K tile, V tile)
 constexpr int PF_OFF_P = PF_OFF_KV + PF_STAGES * 2 * PF_TILE;
 constexpr int PF_OFF_SC = PF_OFF_P + PF_P_BYTES;       // [stages][2][64] floats
-constexpr int PF_OFF_BAR = PF_OFF_SC + PF_STAGES * 2 * PF_BN * 4;
+constexpr int PF_OFF_FAC = PF_OFF_SC + PF_STAGES * 2 * PF_BN * 4;   // [2][3][64] floats: per-key factors of a tile
+constexpr int PF_OFF_BAR = PF_OFF_FAC + 2 * 3 * PF_BN * 4;
 constexpr int PF_SMEM = PF_OFF_BAR + 256 + 1024;
 constexpr int PF_TMEM_COLS = 512;
 constexpr int PF_TMEM_S = 0;            // S: columns [0, 64)
@@ -123,6 +124,17 @@ __device__ __forceinline__ void pf_split4(const float (&x)[4], uint32_t &hi, uin
     const __nv_fp8x2_storage_t l23 = __nv_cvt_float2_to_fp8x2(make_float2(x[2] - f23.x, x[3] - f23.y), __NV_SATFINITE, __NV_E4M3);
     hi = (uint32_t)h01 | ((uint32_t)h23 << 16);
     lo = (uint32_t)l01 | ((uint32_t)l23 << 16);
+}
+
+// two non-negative fp32 values (<= 256) -> 16 bits of hi codes and 16 bits of lo codes, through
+// packed f16 arithmetic (f16 holds x to 11 bits, hi + lo keep 8 of them)
+__device__ __forceinline__ void pf_split2_h(float x0, float x1, uint32_t &hi, uint32_t &lo) {
+    const __half2 x = __floats2half2_rn(x0, x1);
+    const __nv_fp8x2_storage_t h = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw *>(&x), __NV_SATFINITE, __NV_E4M3);
+    const __half2 hb = __half2(__nv_cvt_fp8x2_to_halfraw2(h, __NV_E4M3));
+    const __half2 r = __hsub2(x, hb);
+    const __nv_fp8x2_storage_t l = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw *>(&r), __NV_SATFINITE, __NV_E4M3);
+    hi = h; lo = l;
 }
 
 // byte offset of (row, byte) in a [rows][128 B] block with the 128-byte swizzle
@@ -273,11 +285,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         if (lane == 0) mbar_arrive(s_free);                                     // phase 0: "Q staged"
 
         float m_run = -INFINITY, l_run = 0.f;
-        const float qfac = qinv * p.scale_log2;
         bool ok = true;
+        float *sm_fac = reinterpret_cast<float *>(smem + PF_OFF_FAC);
+        const long long qpos_warp_min = p.pos + q0 + warp * 32;                 // lane 0's position
+        const bool warp_has_padding = warp * 32 + 31 >= rows_here;
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int s = i % PF_STAGES;
-            const float *ksc = sm_sc + (s * 2 + 0) * PF_BN, *vsc = sm_sc + (s * 2 + 1) * PF_BN;
+            // per-key factors of this tile, once per CTA: score scale, log2 of the V scale, 1 / V scale
+            float *fac = sm_fac + (i & 1) * 3 * PF_BN;
+            if (!(ok = mbar_wait(&kv_full[s], (i / PF_STAGES) & 1))) break;
+            if (threadIdx.x < PF_BN) {
+                const float kscv = sm_sc[(s * 2 + 0) * PF_BN + threadIdx.x], vscv = sm_sc[(s * 2 + 1) * PF_BN + threadIdx.x];
+                fac[threadIdx.x] = kscv * p.scale_log2;
+                fac[PF_BN + threadIdx.x] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
+                fac[2 * PF_BN + threadIdx.x] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
+            }
+            named_barrier(1, 128);
             if (!(ok = mbar_wait(s_full, i & 1))) break;
             tc_fence_after();
             float sv[PF_BN];
@@ -293,15 +316,25 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free);                                 // S may be overwritten by tile i+1
-            // scores -> exponent domain, mask, row maximum
+            // scores -> exponent domain (t = raw * k_scale * c * q_inv + log2 v_scale), row maximum
             const long long key0 = (long long)i * PF_BN;
             float mt = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < PF_BN; ++c) {
-                const float tval = fmaf(sv[c], ksc[c] * qfac, __log2f(vsc[c]));
-                sv[c] = (key0 + c <= qpos && row_ok) ? tval : -INFINITY;
-                mt = fmaxf(mt, sv[c]);
+            for (int c4 = 0; c4 < PF_BN / 4; ++c4) {
+                const float4 fa = *reinterpret_cast<const float4 *>(fac + c4 * 4);
+                const float4 fb = *reinterpret_cast<const float4 *>(fac + PF_BN + c4 * 4);
+                sv[c4 * 4 + 0] = fmaf(sv[c4 * 4 + 0] * fa.x, qinv, fb.x);
+                sv[c4 * 4 + 1] = fmaf(sv[c4 * 4 + 1] * fa.y, qinv, fb.y);
+                sv[c4 * 4 + 2] = fmaf(sv[c4 * 4 + 2] * fa.z, qinv, fb.z);
+                sv[c4 * 4 + 3] = fmaf(sv[c4 * 4 + 3] * fa.w, qinv, fb.w);
             }
+            if (key0 + PF_BN - 1 > qpos_warp_min || warp_has_padding) {         // the tile crosses this warp's diagonal
+#pragma unroll
+                for (int c = 0; c < PF_BN; ++c)
+                    if (!(key0 + c <= qpos && row_ok)) sv[c] = -INFINITY;
+            }
+#pragma unroll
+            for (int c = 0; c < PF_BN; ++c) mt = fmaxf(mt, sv[c]);
             const float m_new = fmaxf(m_run, mt);
             const float m_safe = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run - m_safe);   // rows with no visible key yet
@@ -324,16 +357,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                 uint32_t hw[4], lw[4];
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    float y[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int kc = c * 16 + w * 4 + e;
-                        const float pv = fast_exp2(sv[kc] - m_safe);
-                        const float vsv = vsc[kc];
-                        lsum += (key0 + kc <= qpos && row_ok) ? __fdividef(pv, vsv) : 0.f;
-                        y[e] = pv * 256.f;
-                    }
-                    pf_split4(y, hw[w], lw[w]);
+                    const float4 fr = *reinterpret_cast<const float4 *>(fac + 2 * PF_BN + c * 16 + w * 4);
+                    const float p0 = fast_exp2(sv[c * 16 + w * 4 + 0] - m_safe), p1 = fast_exp2(sv[c * 16 + w * 4 + 1] - m_safe);
+                    const float p2 = fast_exp2(sv[c * 16 + w * 4 + 2] - m_safe), p3 = fast_exp2(sv[c * 16 + w * 4 + 3] - m_safe);
+                    lsum = fmaf(p0, fr.x, lsum); lsum = fmaf(p1, fr.y, lsum); lsum = fmaf(p2, fr.z, lsum); lsum = fmaf(p3, fr.w, lsum);
+                    uint32_t h01, l01, h23, l23;
+                    pf_split2_h(p0 * 256.f, p1 * 256.f, h01, l01);
+                    pf_split2_h(p2 * 256.f, p3 * 256.f, h23, l23);
+                    hw[w] = h01 | (h23 << 16);
+                    lw[w] = l01 | (l23 << 16);
                 }
                 *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, c * 16)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
                 *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, 64 + c * 16)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
