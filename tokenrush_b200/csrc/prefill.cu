@@ -1,7 +1,7 @@
 // Chunked prefill attention over the FP8 KV cache on the 5th-generation tensor cores
 // (tcgen05.mma, accumulators in tensor memory).
 //
-// One CTA per (128-query block, query head).  Keys stream in tiles of 64 through a 3-stage TMA
+// One CTA per (128-query block, query head).  Keys stream in tiles of 64 through a 4-stage TMA
 // ring; per tile
 //     S[128 x 64]   = (Qhi + Qlo) K^T         tcgen05.mma kind::f8f6f4, K straight from the TMA tile
 //     P             = exp2(S * k_scale * c + log2 v_scale - m)     128 threads, one query row each
@@ -12,8 +12,10 @@
 // the two terms cost what one bf16 pass would.  Per-key scales never touch the codes: the K scale
 // multiplies the fp32 score, the V scale is moved into the exponent of the probability.
 //
-// Warp roles: warps 0-3 softmax / correction / epilogue (thread = query row = TMEM lane),
-// warp 4 TMA producer, warp 5 MMA issuer.  Every wait is bounded.
+// Warp roles: warps 0-7 softmax / correction / epilogue (two warpgroups; thread = one query row
+// = one TMEM lane, and one half of the tile's keys / of the output columns), warp 8 TMA
+// producer, warp 9 MMA issuer.  S is double-buffered in tensor memory, so QK of tile i+1 runs
+// on the tensor pipe while tile i is in softmax.  Every wait is bounded.
 #include "common.cuh"
 #include "tmap.h"
 
@@ -22,8 +24,9 @@ namespace trb {
 constexpr int PF_BM = 128;              // queries per CTA
 constexpr int PF_BN = 64;               // keys per tile
 constexpr int PF_D = 256;               // head dim (bytes per e4m3 row)
-constexpr int PF_STAGES = 3;
-constexpr int PF_THREADS = 192;
+constexpr int PF_STAGES = 4;
+constexpr int PF_SOFTMAX_THREADS = 256;     // two warpgroups: thread = (query row, half of the tile's keys)
+constexpr int PF_THREADS = PF_SOFTMAX_THREADS + 64;   // + TMA warp + MMA warp
 constexpr int PF_TILE = PF_BN * PF_D;   // bytes of one K or V tile
 constexpr int PF_Q_BYTES = PF_BM * PF_D;               // one e4m3 copy of the query block
 constexpr int PF_P_BYTES = PF_BM * 128;                // [128 rows][hi 64 B | lo 64 B]
@@ -32,10 +35,11 @@ constexpr int PF_OFF_KV = 2 * PF_Q_BYTES;              // stages of (K tile, V t
 constexpr int PF_OFF_P = PF_OFF_KV + PF_STAGES * 2 * PF_TILE;
 constexpr int PF_OFF_SC = PF_OFF_P + PF_P_BYTES;       // [stages][2][64] floats
 constexpr int PF_OFF_FAC = PF_OFF_SC + PF_STAGES * 2 * PF_BN * 4;   // [2][3][64] floats: per-key factors of a tile
-constexpr int PF_OFF_BAR = PF_OFF_FAC + 2 * 3 * PF_BN * 4;
+constexpr int PF_OFF_MX = PF_OFF_FAC + 2 * 3 * PF_BN * 4;          // [2][2][128] floats: row maxima of the two key halves
+constexpr int PF_OFF_BAR = PF_OFF_MX + 2 * 2 * PF_BM * 4;
 constexpr int PF_SMEM = PF_OFF_BAR + 256 + 1024;
 constexpr int PF_TMEM_COLS = 512;
-constexpr int PF_TMEM_S = 0;            // S: columns [0, 64)
+constexpr int PF_TMEM_S = 0;            // S: two buffers, columns [0, 64) and [64, 128)
 constexpr int PF_TMEM_O = 256;          // O: columns [256, 512)
 
 struct PrefillParams {
@@ -147,10 +151,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     extern __shared__ uint8_t pf_smem_raw[];
     uint8_t *smem = pf_smem_raw + ((1024u - (smem_u32(pf_smem_raw) & 1023u)) & 1023u);
     float *sm_sc = reinterpret_cast<float *>(smem + PF_OFF_SC);
+    float *sm_fac = reinterpret_cast<float *>(smem + PF_OFF_FAC);
+    float *sm_mx = reinterpret_cast<float *>(smem + PF_OFF_MX);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + PF_OFF_BAR);
     uint64_t *kv_full = bars, *kv_free = bars + PF_STAGES;
-    uint64_t *s_full = bars + 2 * PF_STAGES, *s_free = s_full + 1, *p_full = s_full + 2, *o_done = s_full + 3;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * PF_STAGES + 4);
+    uint64_t *s_full = bars + 2 * PF_STAGES, *s_free = s_full + 2, *p_full = s_full + 4, *o_done = s_full + 5, *q_ready = s_full + 6;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_full + 7);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = blockIdx.x, h = blockIdx.y, j = h / p.g;
@@ -162,7 +168,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PF_STAGES; ++s) { mbar_init(&kv_full[s], 33u); mbar_init(&kv_free[s], 1u); }
-        mbar_init(s_full, 1u); mbar_init(s_free, 4u); mbar_init(p_full, 4u); mbar_init(o_done, 1u);
+        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1u); mbar_init(&s_free[b], 8u); }
+        mbar_init(p_full, 8u); mbar_init(o_done, 1u); mbar_init(q_ready, 8u);
         mbar_fence_init();
         tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
     }
@@ -172,7 +179,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ================================ TMA producer ================================
         for (int i = 0; i < n_tiles; ++i) {
             const int s = i % PF_STAGES;
@@ -197,19 +204,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             }
             cp_async_mbar_arrive_noinc(&kv_full[s]);
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ================================ MMA issuer ==================================
-        // the query block must be in shared memory first (written by warps 0-3 before p_full's
-        // very first phase is used as "Q ready": they arrive on s_free once at start)
+        // order on the tensor pipe: QK(0), QK(1), PV(0), QK(2), PV(1), ...  S is double-buffered so
+        // that QK(i+1) runs while the softmax warps work on tile i.
         const uint32_t q_hi = smem_u32(smem + PF_OFF_Q), q_lo = q_hi + PF_Q_BYTES;
         const uint32_t p_sm = smem_u32(smem + PF_OFF_P);
         constexpr uint32_t IDESC_QK = umma_idesc_f8(PF_BN, false), IDESC_PV = umma_idesc_f8(PF_D, true);
-        bool ok = mbar_wait(s_free, 0);                                       // Q staged, S free
-        for (int i = 0; i < n_tiles && ok; ++i) {
-            const int s = i % PF_STAGES;
-            const uint32_t kt = smem_u32(smem + PF_OFF_KV + s * 2 * PF_TILE), vt = kt + PF_TILE;
-            if (!(ok = mbar_wait(&kv_full[s], (i / PF_STAGES) & 1))) break;
-            if (i > 0 && !(ok = mbar_wait(s_free, i & 1))) break;               // softmax has read S of tile i-1
+        auto issue_qk = [&](int i) -> bool {
+            const int s = i % PF_STAGES, b = i & 1;
+            const uint32_t kt = smem_u32(smem + PF_OFF_KV + s * 2 * PF_TILE);
+            if (!mbar_wait(&kv_full[s], (i / PF_STAGES) & 1)) return false;
+            if (i >= 2 && !mbar_wait(&s_free[b], ((i >> 1) & 1) ^ 1)) return false;   // softmax has read S of tile i-2
             tc_fence_after();
             if (lane == 0) {
                 // S = Qhi K^T + Qlo K^T : 2 column blocks x 4 k-steps of 32 bytes, hi then lo
@@ -220,12 +226,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
                             const uint64_t a = umma_desc((term ? q_lo : q_hi) + sg * (PF_BM * 128) + k * 32, 16, 1024);
-                            const uint64_t b = umma_desc(kt + sg * (PF_BN * 128) + k * 32, 16, 1024);
-                            tc_mma_f8(tmem + PF_TMEM_S, a, b, IDESC_QK, (term | sg | k) ? 1u : 0u);
+                            const uint64_t bd = umma_desc(kt + sg * (PF_BN * 128) + k * 32, 16, 1024);
+                            tc_mma_f8(tmem + PF_TMEM_S + b * PF_BN, a, bd, IDESC_QK, (term | sg | k) ? 1u : 0u);
                         }
-                tc_commit(s_full);
+                tc_commit(&s_full[b]);
             }
             __syncwarp();
+            return true;
+        };
+        bool ok = mbar_wait(q_ready, 0);                                      // query block staged
+        if (ok && n_tiles > 0) ok = issue_qk(0);
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int s = i % PF_STAGES;
+            const uint32_t vt = smem_u32(smem + PF_OFF_KV + s * 2 * PF_TILE) + PF_TILE;
+            if (i + 1 < n_tiles && !(ok = issue_qk(i + 1))) break;
             if (!(ok = mbar_wait(p_full, i & 1))) break;                        // P of tile i staged (and O corrected)
             tc_fence_after();
             if (lane == 0) {
@@ -235,8 +249,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
                     for (int k = 0; k < 2; ++k) {
                         const uint64_t a = umma_desc(p_sm + term * 64 + k * 32, 16, 1024);
-                        const uint64_t b = umma_desc(vt + k * (32 * 128), PF_BN * 128, 1024);
-                        tc_mma_f8(tmem + PF_TMEM_O, a, b, IDESC_PV, (i | term | k) ? 1u : 0u);
+                        const uint64_t bd = umma_desc(vt + k * (32 * 128), PF_BN * 128, 1024);
+                        tc_mma_f8(tmem + PF_TMEM_O, a, bd, IDESC_PV, (i | term | k) ? 1u : 0u);
                     }
                 tc_commit(&kv_free[s]);
                 tc_commit(o_done);
@@ -244,12 +258,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             __syncwarp();
         }
     } else {
-        // ====================== softmax / correction / epilogue (warps 0-3) ======================
-        const int row = warp * 32 + lane;                                     // query row = TMEM lane
+        // ============ softmax / correction / epilogue: warps 0-7, thread = (row, key half) ============
+        const int row = (warp & 3) * 32 + lane;                               // query row = TMEM lane
+        const int half = warp >> 2;                                           // keys [32 half, 32 half + 32) of a tile
         const bool row_ok = row < rows_here;
         const long long qpos = p.pos + q0 + row;
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-        // ---- stage the query block as two e4m3 copies (power-of-two row scale, hi + lo)
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const int tid = threadIdx.x;                                          // 0..255
+        // ---- stage the query block as two e4m3 copies (power-of-two row scale, hi + lo): both
+        // threads of a row find the row maximum, each converts its 128 dims
         float qinv = 1.f;
         {
             const __nv_bfloat16 *qp = p.q + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D;
@@ -265,7 +282,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             if (e > 90) e = 90;
             const float sc = row_ok ? __uint_as_float((uint32_t)(127 + 7 - e) << 23) : 0.f;
             qinv = __uint_as_float((uint32_t)(127 - 7 + e) << 23);
-            for (int c = 0; c < PF_D / 16; ++c) {                              // 16 dims -> one 16-byte chunk of codes
+            for (int cc = 0; cc < PF_D / 32; ++cc) {                           // this thread's 8 chunks of 16 dims
+                const int c = half * (PF_D / 32) + cc;
                 uint32_t hw[4], lw[4];
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
@@ -282,82 +300,78 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         }
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(s_free);                                     // phase 0: "Q staged"
+        if (lane == 0) mbar_arrive(q_ready);
 
-        float m_run = -INFINITY, l_run = 0.f;
+        float m_run = -INFINITY, l_run = 0.f;                                  // l_run: this thread's half of the keys
         bool ok = true;
-        float *sm_fac = reinterpret_cast<float *>(smem + PF_OFF_FAC);
-        const long long qpos_warp_min = p.pos + q0 + warp * 32;                 // lane 0's position
-        const bool warp_has_padding = warp * 32 + 31 >= rows_here;
+        const long long qpos_warp_min = p.pos + q0 + (warp & 3) * 32;            // lane 0's position
+        const bool warp_has_padding = (warp & 3) * 32 + 31 >= rows_here;
         for (int i = 0; i < n_tiles && ok; ++i) {
-            const int s = i % PF_STAGES;
+            const int s = i % PF_STAGES, b = i & 1;
             // per-key factors of this tile, once per CTA: score scale, log2 of the V scale, 1 / V scale
-            float *fac = sm_fac + (i & 1) * 3 * PF_BN;
+            float *fac = sm_fac + b * 3 * PF_BN;
+            float *mxbuf = sm_mx + b * 2 * PF_BM;
             if (!(ok = mbar_wait(&kv_full[s], (i / PF_STAGES) & 1))) break;
-            if (threadIdx.x < PF_BN) {
-                const float kscv = sm_sc[(s * 2 + 0) * PF_BN + threadIdx.x], vscv = sm_sc[(s * 2 + 1) * PF_BN + threadIdx.x];
-                fac[threadIdx.x] = kscv * p.scale_log2;
-                fac[PF_BN + threadIdx.x] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
-                fac[2 * PF_BN + threadIdx.x] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
+            if (tid < PF_BN) {
+                const float kscv = sm_sc[(s * 2 + 0) * PF_BN + tid], vscv = sm_sc[(s * 2 + 1) * PF_BN + tid];
+                fac[tid] = kscv * p.scale_log2;
+                fac[PF_BN + tid] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
+                fac[2 * PF_BN + tid] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
             }
-            named_barrier(1, 128);
-            if (!(ok = mbar_wait(s_full, i & 1))) break;
+            named_barrier(1, PF_SOFTMAX_THREADS);
+            if (!(ok = mbar_wait(&s_full[b], (i >> 1) & 1))) break;
             tc_fence_after();
-            float sv[PF_BN];
-            {
-                float tmp[32];
-                tmem_ld32(lane_addr + PF_TMEM_S, tmp);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) sv[c] = tmp[c];
-                tmem_ld32(lane_addr + PF_TMEM_S + 32, tmp);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) sv[32 + c] = tmp[c];
-            }
+            float sv[32];
+            tmem_ld32(lane_addr + PF_TMEM_S + b * PF_BN + half * 32, sv);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(s_free);                                 // S may be overwritten by tile i+1
+            if (lane == 0) mbar_arrive(&s_free[b]);                             // this S buffer may be overwritten by tile i+2
             // scores -> exponent domain (t = raw * k_scale * c * q_inv + log2 v_scale), row maximum
-            const long long key0 = (long long)i * PF_BN;
-            float mt = -INFINITY;
+            const long long key0 = (long long)i * PF_BN + half * 32;
+            const float *fa_ = fac + half * 32, *fb_ = fac + PF_BN + half * 32, *fr_ = fac + 2 * PF_BN + half * 32;
 #pragma unroll
-            for (int c4 = 0; c4 < PF_BN / 4; ++c4) {
-                const float4 fa = *reinterpret_cast<const float4 *>(fac + c4 * 4);
-                const float4 fb = *reinterpret_cast<const float4 *>(fac + PF_BN + c4 * 4);
+            for (int c4 = 0; c4 < 8; ++c4) {
+                const float4 fa = *reinterpret_cast<const float4 *>(fa_ + c4 * 4);
+                const float4 fb = *reinterpret_cast<const float4 *>(fb_ + c4 * 4);
                 sv[c4 * 4 + 0] = fmaf(sv[c4 * 4 + 0] * fa.x, qinv, fb.x);
                 sv[c4 * 4 + 1] = fmaf(sv[c4 * 4 + 1] * fa.y, qinv, fb.y);
                 sv[c4 * 4 + 2] = fmaf(sv[c4 * 4 + 2] * fa.z, qinv, fb.z);
                 sv[c4 * 4 + 3] = fmaf(sv[c4 * 4 + 3] * fa.w, qinv, fb.w);
             }
-            if (key0 + PF_BN - 1 > qpos_warp_min || warp_has_padding) {         // the tile crosses this warp's diagonal
+            if (key0 + 31 > qpos_warp_min || warp_has_padding) {               // the tile crosses this warp's diagonal
 #pragma unroll
-                for (int c = 0; c < PF_BN; ++c)
+                for (int c = 0; c < 32; ++c)
                     if (!(key0 + c <= qpos && row_ok)) sv[c] = -INFINITY;
             }
+            float mt = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < PF_BN; ++c) mt = fmaxf(mt, sv[c]);
+            for (int c = 0; c < 32; ++c) mt = fmaxf(mt, sv[c]);
+            mxbuf[half * PF_BM + row] = mt;
+            named_barrier(1, PF_SOFTMAX_THREADS);
+            mt = fmaxf(mt, mxbuf[(half ^ 1) * PF_BM + row]);
             const float m_new = fmaxf(m_run, mt);
             const float m_safe = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run - m_safe);   // rows with no visible key yet
             // the previous PV must have landed before P is overwritten or O is corrected
             if (i > 0 && !(ok = mbar_wait(o_done, (i - 1) & 1))) break;
             tc_fence_after();
-            if (__any_sync(0xffffffffu, alpha != 1.f) && i > 0) {
+            if (__any_sync(0xffffffffu, alpha != 1.f) && i > 0) {               // this thread corrects its 128 columns
 #pragma unroll 1
-                for (int c = 0; c < PF_D / 32; ++c) {
+                for (int c = 0; c < PF_D / 64; ++c) {
                     float ov[32];
-                    tmem_ld32(lane_addr + PF_TMEM_O + c * 32, ov);
+                    tmem_ld32(lane_addr + PF_TMEM_O + half * (PF_D / 2) + c * 32, ov);
 #pragma unroll
                     for (int e = 0; e < 32; ++e) ov[e] *= alpha;
-                    tmem_st32(lane_addr + PF_TMEM_O + c * 32, ov);
+                    tmem_st32(lane_addr + PF_TMEM_O + half * (PF_D / 2) + c * 32, ov);
                 }
             }
             float lsum = 0.f;
 #pragma unroll
-            for (int c = 0; c < PF_BN / 16; ++c) {                              // 16 keys -> one chunk of hi and of lo codes
+            for (int c = 0; c < 2; ++c) {                                       // 16 keys -> one chunk of hi and of lo codes
                 uint32_t hw[4], lw[4];
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    const float4 fr = *reinterpret_cast<const float4 *>(fac + 2 * PF_BN + c * 16 + w * 4);
+                    const float4 fr = *reinterpret_cast<const float4 *>(fr_ + c * 16 + w * 4);
                     const float p0 = fast_exp2(sv[c * 16 + w * 4 + 0] - m_safe), p1 = fast_exp2(sv[c * 16 + w * 4 + 1] - m_safe);
                     const float p2 = fast_exp2(sv[c * 16 + w * 4 + 2] - m_safe), p3 = fast_exp2(sv[c * 16 + w * 4 + 3] - m_safe);
                     lsum = fmaf(p0, fr.x, lsum); lsum = fmaf(p1, fr.y, lsum); lsum = fmaf(p2, fr.z, lsum); lsum = fmaf(p3, fr.w, lsum);
@@ -367,8 +381,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                     hw[w] = h01 | (h23 << 16);
                     lw[w] = l01 | (l23 << 16);
                 }
-                *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, c * 16)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, 64 + c * 16)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, half * 32 + c * 16)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, 64 + half * 32 + c * 16)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
             }
             l_run = fmaf(l_run, alpha, lsum);
             m_run = m_new;
@@ -377,16 +391,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
-        // ---- epilogue: O / (256 * l) -> bf16
+        // ---- epilogue: O / (256 * l) -> bf16; l = sum of the two halves' partial sums
         if (ok && n_tiles > 0) ok = mbar_wait(o_done, (n_tiles - 1) & 1);
         tc_fence_after();
+        sm_mx[half * PF_BM + row] = l_run;
+        named_barrier(1, PF_SOFTMAX_THREADS);
+        const float l_tot = l_run + sm_mx[(half ^ 1) * PF_BM + row];
         if (ok) {
-            const float inv = 1.f / (l_run * 256.f);
-            __nv_bfloat16 *op = p.out + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D;
+            const float inv = 1.f / (l_tot * 256.f);
+            __nv_bfloat16 *op = p.out + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D + half * (PF_D / 2);
 #pragma unroll 1
-            for (int c = 0; c < PF_D / 32; ++c) {
+            for (int c = 0; c < PF_D / 64; ++c) {
                 float ov[32];
-                tmem_ld32(lane_addr + PF_TMEM_O + c * 32, ov);
+                tmem_ld32(lane_addr + PF_TMEM_O + half * (PF_D / 2) + c * 32, ov);
                 if (row_ok) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
