@@ -4,8 +4,8 @@ device-side commit, the DFlash ring / window attention, chunked prefill attentio
 sequence-sharded decode over NVLink.  Host code is Python + PyTorch (tensors, streams,
 torch.distributed); all GPU work is hand-written CUDA behind the C ABI in include/trb_kv.h.
 """
-from . import _lib, config, fused, state            # noqa: F401
+from . import _lib, config, fused, ops, state       # noqa: F401
 from .config import AttnConfig                      # noqa: F401
 from .state import State                            # noqa: F401
 
-__all__ = ["fused", "state", "config", "AttnConfig", "State"]
+__all__ = ["fused", "ops", "state", "config", "AttnConfig", "State"]

@@ -39,6 +39,8 @@ def _need_cuda(*ts):
 
 def _cursor(pos) -> L.Cursor:
     """A python int, or a device tensor of one int32 / int64 (State.pos_t)."""
+    if isinstance(pos, L.Cursor):
+        return pos
     if isinstance(pos, torch.Tensor):
         if pos.dtype not in (torch.int32, torch.int64) or pos.numel() < 1:
             raise TypeError("position tensor must be int32 or int64")
