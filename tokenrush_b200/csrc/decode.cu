@@ -213,15 +213,20 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             // f16 copies of the bf16 query (exact for |q| < 65504): word [h][w] of chunk pair cp holds
             // dims 32cp + 16w + 4t + 2h, +1, the k-slots that the low / high half-words of the
             // ldmatrix registers of K map to
-#pragma unroll 2
+            // all loads first (one round trip), then the conversions
+            uint2 raw[C::NCP][2];
+#pragma unroll
+            for (int cp = 0; cp < C::NCP; ++cp)
+#pragma unroll
+                for (int w = 0; w < 2; ++w)
+                    raw[cp][w] = valid ? __ldg(reinterpret_cast<const uint2 *>(qp + 32 * cp + 16 * w + 4 * t)) : make_uint2(0u, 0u);
+#pragma unroll
             for (int cp = 0; cp < C::NCP; ++cp) {
                 uint32_t f[2][2];
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
-                    uint2 raw = make_uint2(0u, 0u);
-                    if (valid) raw = *reinterpret_cast<const uint2 *>(qp + 32 * cp + 16 * w + 4 * t);
-                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
-                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw[cp][w].x));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw[cp][w].y));
                     f[0][w] = pack_f16x2(a.x, a.y);
                     f[1][w] = pack_f16x2(b.x, b.y);
                 }
@@ -559,6 +564,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (row >= p.rows) break;
         const int qi = row / p.g, hq = j * p.g + row % p.g;
         const long long grow = (long long)qi * p.hq + hq;
+        // one round trip: the (max, sum) pairs of all splits and this thread's first eight slices of
+        // the accumulators are requested together; the weights are applied once both are here
+        const float *pa = p.part_acc + ((long long)j * p.nsplit * p.rows_pad + row) * D + d4;
+        const long long pstride = (long long)p.rows_pad * D;
+        float4 pre[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int sp = grp + u * GROUPS;
+            pre[u] = sp < active ? __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
         for (int sp = tid; sp < n_parts; sp += DEC_CTHREADS) {
             float2 v;
             if (sp < active) v = __ldcg(reinterpret_cast<const float2 *>(&p.part_ml[(((long long)j * p.nsplit + sp) * p.rows_pad + row) * 2]));
@@ -572,10 +587,16 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         for (int sp = lane; sp < n_parts; sp += 32) lsum += sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax) * sm_l[sp];
         lsum = warp_sum(lsum);
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-        const float *pa = p.part_acc + ((long long)j * p.nsplit * p.rows_pad + row) * D + d4;
-        const long long pstride = (long long)p.rows_pad * D;
-#pragma unroll 8
-        for (int sp = grp; sp < active; sp += GROUPS) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {                                      // split order within the group: ascending
+            const int sp = grp + u * GROUPS;
+            if (sp < active) {
+                const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
+                o.x = fmaf(w, pre[u].x, o.x); o.y = fmaf(w, pre[u].y, o.y); o.z = fmaf(w, pre[u].z, o.z); o.w = fmaf(w, pre[u].w, o.w);
+            }
+        }
+#pragma unroll 4
+        for (int sp = grp + 8 * GROUPS; sp < active; sp += GROUPS) {
             const float4 v = __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride));
             const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
             o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
