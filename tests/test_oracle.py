@@ -74,6 +74,10 @@ def test_decode_and_verify_attention_vs_reference(golden_dir):
     np.testing.assert_allclose(o1, z["out_m1"], rtol=0, atol=1e-6)
     o5 = O.decode_step_cpu(st, 0, qb, kb[:, L0:], vb[:, L0:], L0)
     np.testing.assert_allclose(o5, z["out_m5"], rtol=0, atol=1e-6)
+    # the threaded form that the CPU baseline is timed on gives the same numbers
+    o5t = O.decode_step_cpu_threaded(st, 0, qb, kb[:, L0:], vb[:, L0:], L0)
+    np.testing.assert_allclose(o5t, z["out_m5"], rtol=0, atol=1e-6)
+    np.testing.assert_allclose(o5t, o5, rtol=0, atol=1e-6)
     # row i of an M-row step equals a 1-row step at position L0 + i (tests/test_fused.py:97-122)
     kd, vd = st.dequant(0, L0 + 5)
     for i in range(5):

@@ -20,8 +20,15 @@
 //   * online softmax in registers with warp shuffles; every warp keeps its own running
 //     (max, sum, acc) and the warps of a CTA, the CTAs of a kv head and (for sequence
 //     shards) the GPUs are all merged with the same log-sum-exp formula in a fixed order;
-//   * the last CTA of a kv head to finish (an atomic ticket that resets itself, so the
-//     launch replays inside a CUDA graph) merges the split partials and writes the output.
+//   * every CTA writes one (max, sum, acc) partial per row and takes an atomic ticket of its
+//     kv head; the last arrival resets the counters (so the launch replays inside a CUDA
+//     graph) and publishes an epoch.  The last `rows` arrivals stay (bounded wait on the
+//     epoch) and claim output rows one at a time: a row's split partials are fetched in one
+//     round trip, merged in split order, gated if asked, and written as bf16 - or, for a
+//     sequence shard, pushed to the peers' exchange buffers and merged in rank order.  The
+//     last arrival claims until no row is left, so completeness never needs co-residency.
+//   * programmatic dependent launch: tiles that the preceding append cannot touch are
+//     requested before griddepcontrol.wait, so the prologue overlaps the append's tail.
 //
 // The live length and all split ranges are derived on the device from the cursor, so the
 // grid is static and one captured graph serves every length.
