@@ -80,6 +80,14 @@ const char *trb_strerror(int code);
  * switches to ordinary launches (also: environment variable TRB_PDL=0). */
 int trb_set_programmatic_launch(int enable);
 
+/* trb_attn_decode has two kernels for FP8 caches of head dim 256 without ring or window: a
+ * mma.sync kernel (any M; the bandwidth kernel for M = 1) and a tcgen05 kernel that keeps the
+ * tensor work off the issue slots when several query rows share a kv head (speculative verify).
+ * The second one runs when (hq / hkv) * m >= min_rows.  min_rows <= 0 restores the default (12,
+ * i.e. M >= 2 at 24/4 heads); a value above 48 keeps every call on the first kernel.  Both give
+ * results within the same tolerance; the switch exists for testing and measurement. */
+int trb_set_decode_tensor_rows(int32_t min_rows);
+
 /* Read and clear the device status word of the current device.  Synchronises the device:
  * call it outside graph capture. */
 int trb_device_status(uint32_t *status_out);

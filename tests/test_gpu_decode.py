@@ -88,9 +88,18 @@ def test_decode_m1_lengths(tb, L):
     assert_attn_close(o32.reshape(1, HQ, D), _oracle_step(st, qb, L), f"fp32 L={L}", out_ulp=0.0)
 
 
+@pytest.fixture(params=["tensor", "mma"])
+def verify_kernel(request, tb):
+    """Runs a test once on each decode kernel for M > 1: the tcgen05 one (default from 12 query
+    rows per kv head) and the mma.sync one (forced by raising the switch above the maximum)."""
+    tb._lib.lib().trb_set_decode_tensor_rows(49 if request.param == "mma" else 0)
+    yield request.param
+    tb._lib.lib().trb_set_decode_tensor_rows(0)
+
+
 @pytest.mark.parametrize("M", [2, 3, 4, 5, 6, 7, 8])
 @pytest.mark.parametrize("L", [5, 1100])
-def test_verify_rows_match_oracle_and_sequential(tb, M, L):
+def test_verify_rows_match_oracle_and_sequential(tb, M, L, verify_kernel):
     cfg, st = _filled_state(tb, L, L + 64, seed=77)
     qb = O.seeded_bf16(6, M, HQ, D)
     kb, vb = O.seeded_bf16(7, HKV, M, D), O.seeded_bf16(8, HKV, M, D)
@@ -102,6 +111,84 @@ def test_verify_rows_match_oracle_and_sequential(tb, M, L):
         oi = tb.fused.attn_decode_fused(to_dev(qb[i:i + 1]).reshape(1, -1), None, st.k[0], st.v[0], st.pos_t, cfg,
                                         st.k_scale[0], st.v_scale[0])
         assert rel(f32_of(oi).reshape(HQ, D), o[i]) < 5e-3
+
+
+@pytest.mark.parametrize("M,L", [(8, 0), (8, 120), (8, 121), (8, 127), (8, 128), (4, 255), (2, 383), (8, 4736), (5, 20000), (8, 40000)])
+def test_verify_tile_edges_and_many_splits(tb, M, L, verify_kernel):
+    """Lengths around the 128-key tiles of the tensor-core kernel, one tile per split up to many
+    tiles per split; the un-rounded fp32 (max, sum, acc) output is checked at the flat 2e-3 bar.
+    (The tensor-core kernel carries its softmax weights with 8 significant bits, as the bf16
+    output does; with fewer than a few dozen keys per row nothing averages that out, and the bar
+    there is the one of the bf16 output.)"""
+    cfg, st = _filled_state(tb, L, L + 64, seed=300 + M)
+    qb = O.seeded_bf16(31, M, HQ, D)
+    kb, vb = O.seeded_bf16(32, HKV, M, D), O.seeded_bf16(33, HKV, M, D)
+    o = f32_of(_step(tb, cfg, st, qb, kb, vb)).reshape(M, HQ, D)
+    want = _oracle_step(st, qb, L)
+    assert_attn_close(o, want, f"{verify_kernel} M={M} L={L}")
+    ml, acc = tb.fused.attn_decode_fused(to_dev(qb).reshape(M, -1), None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0],
+                                         st.v_scale[0], partial=True)
+    o32 = (acc / ml[:, 1:2]).float().cpu().numpy().reshape(M, HQ, D)
+    assert_attn_close(o32, want, f"{verify_kernel} fp32 M={M} L={L}", out_ulp=2.0 ** -8 if (verify_kernel == "tensor" and L < 64) else 0.0)
+    assert tb._lib.device_status() == 0
+
+
+def test_verify_peaked_rows_and_gate(tb, verify_kernel):
+    """Eight rows with queries scaled x6 (peaked softmax, row maxima that keep moving between
+    tiles) and planted keys in the first, a middle and the last tile; the sigmoid gate fused in
+    the tail."""
+    M, L = 8, 6000
+    cfg, st = _filled_state(tb, L, L + 64, seed=41)
+    qb = O.f32_to_bf16_bits(O.bf16_bits_to_f32(O.seeded_bf16(34, M, HQ, D)) * 6.0)
+    q = O.bf16_bits_to_f32(qb)
+    for n, pos_plant in enumerate((3, 2900, 5999)):
+        krow = np.stack([q[n, j * 6 + n] * 0.5 for j in range(HKV)])[:, None, :]
+        tb.fused.kv_write_prefill(to_dev(O.f32_to_bf16_bits(krow)), to_dev(O.seeded_bf16(35 + n, HKV, 1, D)), st, 0, pos_plant)
+    kb, vb = O.seeded_bf16(38, HKV, M, D), O.seeded_bf16(39, HKV, M, D)
+    o = f32_of(_step(tb, cfg, st, qb, kb, vb)).reshape(M, HQ, D)
+    want = _oracle_step(st, qb, L)
+    assert_attn_close(o, want, f"{verify_kernel} peaked M=8")
+    gb = O.seeded_bf16(40, M, HQ, D)
+    qkv = np.zeros((M, HQ * 2 * D + 2 * HKV * D), dtype=np.uint16)
+    qkv[:, :HQ * 2 * D].reshape(M, HQ, 2 * D)[:, :, D:] = gb
+    og = tb.fused.attn_decode_fused(to_dev(qb).reshape(M, -1), to_dev(qkv), st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0],
+                                    st.v_scale[0])
+    # the gate is applied to the bf16-rounded output, as the oracle composes it
+    assert_attn_close(f32_of(og).reshape(M, HQ, D), O.bf16_bits_to_f32(O.gate_output(o, gb)), f"{verify_kernel} gated", out_ulp=2.0 ** -7)
+    assert tb._lib.device_status() == 0
+
+
+def test_verify_graph_replay_is_reproducible(tb, verify_kernel):
+    """An 8-row verify step captured once and replayed at growing lengths read from the device
+    cursor: every replay matches the oracle, and the same length gives the same bits."""
+    M, L0 = 8, 700
+    cfg, st = _filled_state(tb, L0, 2048, seed=55)
+    qb = O.seeded_bf16(45, M, HQ, D)
+    kb, vb = O.seeded_bf16(46, HKV, M, D), O.seeded_bf16(47, HKV, M, D)
+    dq, dk, dv = to_dev(qb).reshape(M, -1), to_dev(kb), to_dev(vb)
+    out = torch.empty(M, HQ * D, dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        tb.fused.kv_write_prefill(dk, dv, st, 0, st.pos_t)
+        tb.fused.attn_decode_fused(dq, None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0], st.v_scale[0], out=out)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        step()
+        torch.cuda.current_stream().synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            step()
+    seen = {}
+    for L in (L0, L0 + 3, L0 + 120, L0 + 3):
+        st.set_pos(L)
+        g.replay()
+        torch.cuda.synchronize()
+        o = out.clone()
+        assert_attn_close(f32_of(o).reshape(M, HQ, D), _oracle_step(st, qb, L), f"{verify_kernel} replay L={L}")
+        if L in seen:
+            assert torch.equal(seen[L], o)
+        seen[L] = o
+    assert tb._lib.device_status() == 0
 
 
 def test_decode_peaked_distribution_and_planted_keys(tb):

@@ -56,6 +56,7 @@ SIGNATURES = {
     "trb_version": (C.c_int, []),
     "trb_strerror": (C.c_char_p, [C.c_int]),
     "trb_set_programmatic_launch": (C.c_int, [C.c_int]),
+    "trb_set_decode_tensor_rows": (C.c_int, [C.c_int32]),
     "trb_device_status": (C.c_int, [C.POINTER(C.c_uint32)]),
     "trb_kv_append": (C.c_int, [C.POINTER(Cache), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,
                                 C.POINTER(Cursor), C.POINTER(Cursor), C.c_void_p]),

@@ -107,6 +107,201 @@ __device__ __forceinline__ int acc_dim(int a, int i, int g) {
     return 16 * a + 8 * (i >> 1) + g;
 }
 
+// Ticket and tail shared by the decode kernels.  Called by every thread of the CTA once the
+// CTA's partial (max, sum, acc) rows are written to the workspace.  `smem` is scratch from its
+// start (at least 6 KB), `sm_flag` three ints outside that scratch.
+template <int D, int NTHREADS>
+__device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem, int *sm_flag, const int j, const int active,
+                                            const unsigned int epoch) {
+    const int tid = threadIdx.x, lane = threadIdx.x & 31;
+    // 2. ticket.  The last CTA of this kv head to arrive publishes a new epoch; CTAs that arrived
+    // earlier wait for it (bounded) and then every CTA present claims output rows one at a time
+    // and merges them, so the combine runs on many SMs.  The last CTA keeps claiming until no
+    // row is left, so the result is complete even if every helper gave up waiting.
+    unsigned int *ticket = p.counters + j, *claim = p.counters + 64 + j, *seq = p.counters + 128 + j;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int old = atomicAdd(ticket, 1u);
+        int state = old == (unsigned int)(active - 1) ? 2 : 1;
+        if (state == 2) {
+            *ticket = 0u;                                               // ready for the next launch / replay
+            *claim = 0u;
+            __threadfence();
+            *(volatile unsigned int *)seq = epoch + 1u;
+        } else {
+            state = 0;
+            // only the last `rows` arrivals can find a row to merge; earlier ones leave at once and
+            // free their SM for the next kernel in the stream
+            for (int it = 0; it < 4096 && (int)old >= active - p.rows; ++it) {
+                if (*(volatile unsigned int *)seq == epoch + 1u) { state = 1; break; }
+                __nanosleep(100);
+            }
+        }
+        *sm_flag = state;
+        sm_flag[2] = (int)epoch;
+    }
+    __syncthreads();
+    if (*sm_flag == 0) return;                                          // gave up waiting: the others finish the rows
+    __threadfence();
+
+    // 3. tail: LSE merge of one output row per claim over the active splits (+ extra partials), in
+    // split order: thread (item, group) sums the splits of its group, the groups are added in
+    // group order through shared memory.
+    const int n_parts = active + p.n_extra;
+    constexpr int ITEMS = D / 4, GROUPS = NTHREADS / ITEMS;
+    float *sm_m = reinterpret_cast<float *>(smem);                      // [n_parts]
+    float *sm_l = sm_m + (DEC_MAX_SPLITS + 4);                          // [n_parts]
+    float4 *sm_red = reinterpret_cast<float4 *>(sm_l + (DEC_MAX_SPLITS + 4));   // [GROUPS][ITEMS]
+    int *sm_claim = sm_flag + 1;
+    const int item = tid % ITEMS, grp = tid / ITEMS, d4 = item * 4;
+    for (;;) {
+        __syncthreads();
+        if (tid == 0) *sm_claim = (int)atomicAdd(claim, 1u);
+        __syncthreads();
+        const int row = *sm_claim;
+        if (row >= p.rows) break;
+        const int qi = row / p.g, hq = j * p.g + row % p.g;
+        const long long grow = (long long)qi * p.hq + hq;
+        // one round trip: the (max, sum) pairs of all splits and this thread's first eight slices of
+        // the accumulators are requested together; the weights are applied once both are here
+        const float *pa = p.part_acc + ((long long)j * p.nsplit * p.rows_pad + row) * D + d4;
+        const long long pstride = (long long)p.rows_pad * D;
+        float4 pre[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int sp = grp + u * GROUPS;
+            pre[u] = sp < active ? __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int sp = tid; sp < n_parts; sp += NTHREADS) {
+            float2 v;
+            if (sp < active) v = __ldcg(reinterpret_cast<const float2 *>(&p.part_ml[(((long long)j * p.nsplit + sp) * p.rows_pad + row) * 2]));
+            else v = *reinterpret_cast<const float2 *>(&p.extra_ml[(grow * p.n_extra + (sp - active)) * 2]);
+            sm_m[sp] = v.x; sm_l[sp] = v.y;
+        }
+        __syncthreads();
+        float mmax = -INFINITY, lsum = 0.f;
+        for (int sp = lane; sp < n_parts; sp += 32) mmax = fmaxf(mmax, sm_m[sp]);
+        mmax = warp_max(mmax);
+        for (int sp = lane; sp < n_parts; sp += 32) lsum += sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax) * sm_l[sp];
+        lsum = warp_sum(lsum);
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {                                      // split order within the group: ascending
+            const int sp = grp + u * GROUPS;
+            if (sp < active) {
+                const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
+                o.x = fmaf(w, pre[u].x, o.x); o.y = fmaf(w, pre[u].y, o.y); o.z = fmaf(w, pre[u].z, o.z); o.w = fmaf(w, pre[u].w, o.w);
+            }
+        }
+#pragma unroll 4
+        for (int sp = grp + 8 * GROUPS; sp < active; sp += GROUPS) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride));
+            const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
+            o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+        }
+        if (grp == 0)
+            for (int e = 0; e < p.n_extra; ++e) {
+                const float4 v = *reinterpret_cast<const float4 *>(&p.extra_acc[(grow * p.n_extra + e) * D + d4]);
+                const float w = sm_m[active + e] == -INFINITY ? 0.f : fast_exp2(sm_m[active + e] - mmax);
+                o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+            }
+        sm_red[grp * ITEMS + item] = o;
+        __syncthreads();
+        const bool lead = grp == 0;                                      // these threads hold the row from here on
+        if (lead) {
+            for (int k = 1; k < GROUPS; ++k) {
+                const float4 v = sm_red[k * ITEMS + item];
+                o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
+            }
+        }
+        if (p.shard_acc) {
+            if (lead) {
+                *reinterpret_cast<float4 *>(&p.shard_acc[grow * D + d4]) = o;
+                if (item == 0) { p.shard_ml[grow * 2] = mmax; p.shard_ml[grow * 2 + 1] = lsum; }
+            }
+            continue;
+        }
+        if (p.p2p_world > 0) {
+            // ---- sequence shards: exchange this row's (max, sum, acc) with the other GPUs by peer
+            // stores, wait (bounded) for theirs, merge in rank order.  The tag is this kv head's launch
+            // epoch, identical on all GPUs because they make the same calls on their workspaces.
+            // This GPU's own partial stays in registers; only the peers' go through memory.
+            const P2PLayout xl = p2p_layout(p.p2p_world, p.m * p.hq, D);
+            const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
+            const size_t slot = tag % P2P_SLOTS;
+            const size_t nrow = (size_t)(p.m * p.hq);
+            if (lead) {
+                for (int r = 0; r < p.p2p_world; ++r) {
+                    if (r == p.p2p_rank) continue;
+                    float *dst = (float *)((uint8_t *)p.p2p_ptr[r] + xl.data) + ((slot * p.p2p_world + p.p2p_rank) * nrow + grow) * xl.row_floats;
+                    *reinterpret_cast<float4 *>(dst + d4) = o;
+                    if (item == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(mmax, lsum);
+                }
+                __threadfence_system();
+            }
+            __syncthreads();
+            uint8_t *local = (uint8_t *)p.p2p_ptr[p.p2p_rank];
+            if (tid < p.p2p_world && tid != p.p2p_rank) {
+                volatile unsigned int *flag = (volatile unsigned int *)((uint8_t *)p.p2p_ptr[tid] + xl.flags) + (slot * p.p2p_world + p.p2p_rank) * nrow + grow;
+                *flag = tag;
+                const volatile unsigned int *mine = (const volatile unsigned int *)(local + xl.flags) + (slot * p.p2p_world + tid) * nrow + grow;
+                bool ok = false;
+                for (unsigned int it = 0; it < P2P_SPIN_LIMIT; ++it) {
+                    if (*mine == tag) { ok = true; break; }
+                    if (it > 64) __nanosleep(100);
+                }
+                if (!ok) raise_status(TRB_ST_PEER_TIMEOUT);
+                __threadfence_system();
+            }
+            __syncthreads();
+            if (lead && p.p2p_world > 1) {
+                const float *data = (const float *)(local + xl.data);
+                float gm = mmax;
+                for (int r = 0; r < p.p2p_world; ++r)
+                    if (r != p.p2p_rank) gm = fmaxf(gm, __ldcg(data + ((slot * p.p2p_world + r) * nrow + grow) * xl.row_floats + D));
+                float gl = 0.f;
+                float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int r = 0; r < p.p2p_world; ++r) {                  // rank order, own partial from registers
+                    float2 mlr = make_float2(mmax, lsum);
+                    float4 v = o;
+                    if (r != p.p2p_rank) {
+                        const float *src = data + ((slot * p.p2p_world + r) * nrow + grow) * xl.row_floats;
+                        mlr = __ldcg(reinterpret_cast<const float2 *>(src + D));
+                        v = __ldcg(reinterpret_cast<const float4 *>(src + d4));
+                    }
+                    const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
+                    gl = fmaf(w, mlr.y, gl);
+                    go.x = fmaf(w, v.x, go.x); go.y = fmaf(w, v.y, go.y); go.z = fmaf(w, v.z, go.z); go.w = fmaf(w, v.w, go.w);
+                }
+                o = go; lsum = gl;
+            }
+        }
+        if (!lead) continue;
+        const float inv = 1.f / lsum;
+        float r[4] = {o.x * inv, o.y * inv, o.z * inv, o.w * inv};
+        __nv_bfloat16 ob[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ob[e] = __float2bfloat16_rn(r[e]);
+        if (p.gate) {
+            const __nv_bfloat16 *gp = p.gate + (long long)qi * p.gate_rs + (long long)hq * p.gate_hs + d4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float gv = __bfloat162float(gp[e]);
+                const float sg = __bfloat162float(__float2bfloat16_rn(1.f / (1.f + __expf(-gv))));
+                ob[e] = __float2bfloat16_rn(__bfloat162float(ob[e]) * sg);
+            }
+        }
+        *reinterpret_cast<uint2 *>(&p.out[grow * D + d4]) = *reinterpret_cast<const uint2 *>(ob);
+    }
+}
+
+}  // namespace trb
+
+#include "decode_tc.cuh"
+
+namespace trb {
+
 template <int D, bool FP8, int GS>
 __global__ void __launch_bounds__(DEC_THREADS, 1)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
@@ -522,186 +717,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         p.part_ml[(part_base + row) * 2 + 1] = lg;
     }
 
-    // 2. ticket.  The last CTA of this kv head to arrive publishes a new epoch; CTAs that arrived
-    // earlier wait for it (bounded) and then every CTA present claims output rows one at a time
-    // and merges them, so the combine runs on many SMs.  The last CTA keeps claiming until no
-    // row is left, so the result is complete even if every helper gave up waiting.
-    unsigned int *ticket = p.counters + j, *claim = p.counters + 64 + j, *seq = p.counters + 128 + j;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned int old = atomicAdd(ticket, 1u);
-        int state = old == (unsigned int)(active - 1) ? 2 : 1;
-        if (state == 2) {
-            *ticket = 0u;                                               // ready for the next launch / replay
-            *claim = 0u;
-            __threadfence();
-            *(volatile unsigned int *)seq = epoch + 1u;
-        } else {
-            state = 0;
-            // only the last `rows` arrivals can find a row to merge; earlier ones leave at once and
-            // free their SM for the next kernel in the stream
-            for (int it = 0; it < 4096 && (int)old >= active - p.rows; ++it) {
-                if (*(volatile unsigned int *)seq == epoch + 1u) { state = 1; break; }
-                __nanosleep(100);
-            }
-        }
-        *sm_flag = state;
-        sm_flag[2] = (int)epoch;
-    }
-    __syncthreads();
-    if (*sm_flag == 0) return;                                          // gave up waiting: the others finish the rows
-    __threadfence();
-
-    // 3. tail: LSE merge of one output row per claim over the active splits (+ extra partials), in
-    // split order: thread (item, group) sums the splits of its group, the groups are added in
-    // group order through shared memory.
-    const int n_parts = active + p.n_extra;
-    constexpr int ITEMS = D / 4, GROUPS = DEC_CTHREADS / ITEMS;
-    float *sm_m = reinterpret_cast<float *>(smem);                      // [n_parts]
-    float *sm_l = sm_m + (DEC_MAX_SPLITS + 4);                          // [n_parts]
-    float4 *sm_red = reinterpret_cast<float4 *>(sm_l + (DEC_MAX_SPLITS + 4));   // [GROUPS][ITEMS]
-    int *sm_claim = sm_flag + 1;
-    const int item = tid % ITEMS, grp = tid / ITEMS, d4 = item * 4;
-    for (;;) {
-        __syncthreads();
-        if (tid == 0) *sm_claim = (int)atomicAdd(claim, 1u);
-        __syncthreads();
-        const int row = *sm_claim;
-        if (row >= p.rows) break;
-        const int qi = row / p.g, hq = j * p.g + row % p.g;
-        const long long grow = (long long)qi * p.hq + hq;
-        // one round trip: the (max, sum) pairs of all splits and this thread's first eight slices of
-        // the accumulators are requested together; the weights are applied once both are here
-        const float *pa = p.part_acc + ((long long)j * p.nsplit * p.rows_pad + row) * D + d4;
-        const long long pstride = (long long)p.rows_pad * D;
-        float4 pre[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int sp = grp + u * GROUPS;
-            pre[u] = sp < active ? __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        for (int sp = tid; sp < n_parts; sp += DEC_CTHREADS) {
-            float2 v;
-            if (sp < active) v = __ldcg(reinterpret_cast<const float2 *>(&p.part_ml[(((long long)j * p.nsplit + sp) * p.rows_pad + row) * 2]));
-            else v = *reinterpret_cast<const float2 *>(&p.extra_ml[(grow * p.n_extra + (sp - active)) * 2]);
-            sm_m[sp] = v.x; sm_l[sp] = v.y;
-        }
-        __syncthreads();
-        float mmax = -INFINITY, lsum = 0.f;
-        for (int sp = lane; sp < n_parts; sp += 32) mmax = fmaxf(mmax, sm_m[sp]);
-        mmax = warp_max(mmax);
-        for (int sp = lane; sp < n_parts; sp += 32) lsum += sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax) * sm_l[sp];
-        lsum = warp_sum(lsum);
-        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {                                      // split order within the group: ascending
-            const int sp = grp + u * GROUPS;
-            if (sp < active) {
-                const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
-                o.x = fmaf(w, pre[u].x, o.x); o.y = fmaf(w, pre[u].y, o.y); o.z = fmaf(w, pre[u].z, o.z); o.w = fmaf(w, pre[u].w, o.w);
-            }
-        }
-#pragma unroll 4
-        for (int sp = grp + 8 * GROUPS; sp < active; sp += GROUPS) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride));
-            const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
-            o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
-        }
-        if (grp == 0)
-            for (int e = 0; e < p.n_extra; ++e) {
-                const float4 v = *reinterpret_cast<const float4 *>(&p.extra_acc[(grow * p.n_extra + e) * D + d4]);
-                const float w = sm_m[active + e] == -INFINITY ? 0.f : fast_exp2(sm_m[active + e] - mmax);
-                o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
-            }
-        sm_red[grp * ITEMS + item] = o;
-        __syncthreads();
-        const bool lead = grp == 0;                                      // these threads hold the row from here on
-        if (lead) {
-            for (int k = 1; k < GROUPS; ++k) {
-                const float4 v = sm_red[k * ITEMS + item];
-                o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
-            }
-        }
-        if (p.shard_acc) {
-            if (lead) {
-                *reinterpret_cast<float4 *>(&p.shard_acc[grow * D + d4]) = o;
-                if (item == 0) { p.shard_ml[grow * 2] = mmax; p.shard_ml[grow * 2 + 1] = lsum; }
-            }
-            continue;
-        }
-        if (p.p2p_world > 0) {
-            // ---- sequence shards: exchange this row's (max, sum, acc) with the other GPUs by peer
-            // stores, wait (bounded) for theirs, merge in rank order.  The tag is this kv head's launch
-            // epoch, identical on all GPUs because they make the same calls on their workspaces.
-            // This GPU's own partial stays in registers; only the peers' go through memory.
-            const P2PLayout xl = p2p_layout(p.p2p_world, p.m * p.hq, D);
-            const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
-            const size_t slot = tag % P2P_SLOTS;
-            const size_t nrow = (size_t)(p.m * p.hq);
-            if (lead) {
-                for (int r = 0; r < p.p2p_world; ++r) {
-                    if (r == p.p2p_rank) continue;
-                    float *dst = (float *)((uint8_t *)p.p2p_ptr[r] + xl.data) + ((slot * p.p2p_world + p.p2p_rank) * nrow + grow) * xl.row_floats;
-                    *reinterpret_cast<float4 *>(dst + d4) = o;
-                    if (item == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(mmax, lsum);
-                }
-                __threadfence_system();
-            }
-            __syncthreads();
-            uint8_t *local = (uint8_t *)p.p2p_ptr[p.p2p_rank];
-            if (tid < p.p2p_world && tid != p.p2p_rank) {
-                volatile unsigned int *flag = (volatile unsigned int *)((uint8_t *)p.p2p_ptr[tid] + xl.flags) + (slot * p.p2p_world + p.p2p_rank) * nrow + grow;
-                *flag = tag;
-                const volatile unsigned int *mine = (const volatile unsigned int *)(local + xl.flags) + (slot * p.p2p_world + tid) * nrow + grow;
-                bool ok = false;
-                for (unsigned int it = 0; it < P2P_SPIN_LIMIT; ++it) {
-                    if (*mine == tag) { ok = true; break; }
-                    if (it > 64) __nanosleep(100);
-                }
-                if (!ok) raise_status(TRB_ST_PEER_TIMEOUT);
-                __threadfence_system();
-            }
-            __syncthreads();
-            if (lead && p.p2p_world > 1) {
-                const float *data = (const float *)(local + xl.data);
-                float gm = mmax;
-                for (int r = 0; r < p.p2p_world; ++r)
-                    if (r != p.p2p_rank) gm = fmaxf(gm, __ldcg(data + ((slot * p.p2p_world + r) * nrow + grow) * xl.row_floats + D));
-                float gl = 0.f;
-                float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int r = 0; r < p.p2p_world; ++r) {                  // rank order, own partial from registers
-                    float2 mlr = make_float2(mmax, lsum);
-                    float4 v = o;
-                    if (r != p.p2p_rank) {
-                        const float *src = data + ((slot * p.p2p_world + r) * nrow + grow) * xl.row_floats;
-                        mlr = __ldcg(reinterpret_cast<const float2 *>(src + D));
-                        v = __ldcg(reinterpret_cast<const float4 *>(src + d4));
-                    }
-                    const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
-                    gl = fmaf(w, mlr.y, gl);
-                    go.x = fmaf(w, v.x, go.x); go.y = fmaf(w, v.y, go.y); go.z = fmaf(w, v.z, go.z); go.w = fmaf(w, v.w, go.w);
-                }
-                o = go; lsum = gl;
-            }
-        }
-        if (!lead) continue;
-        const float inv = 1.f / lsum;
-        float r[4] = {o.x * inv, o.y * inv, o.z * inv, o.w * inv};
-        __nv_bfloat16 ob[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) ob[e] = __float2bfloat16_rn(r[e]);
-        if (p.gate) {
-            const __nv_bfloat16 *gp = p.gate + (long long)qi * p.gate_rs + (long long)hq * p.gate_hs + d4;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float gv = __bfloat162float(gp[e]);
-                const float sg = __bfloat162float(__float2bfloat16_rn(1.f / (1.f + __expf(-gv))));
-                ob[e] = __float2bfloat16_rn(__bfloat162float(ob[e]) * sg);
-            }
-        }
-        *reinterpret_cast<uint2 *>(&p.out[grow * D + d4]) = *reinterpret_cast<const uint2 *>(ob);
-    }
+    decode_tail<D, DEC_CTHREADS>(p, smem, sm_flag, j, active, epoch);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -835,9 +851,39 @@ static int launch_decode(const CUtensorMap &mk, const CUtensorMap &mv, const Dec
     return decode_groups_per_warp(p.nt) == 2 ? launch_decode_gs<D, FP8, 2>(mk, mv, p, st) : launch_decode_gs<D, FP8, 1>(mk, mv, p, st);
 }
 
+// Query rows per kv head (heads per kv head x M) from which the tensor-core kernel takes FP8
+// caches of head dim 256 without ring or window.
+constexpr int DEC_TC_DEFAULT_MIN_ROWS = 12;
+static int g_tc_min_rows = DEC_TC_DEFAULT_MIN_ROWS;
+
+template <int NROW>
+static int launch_decode_tc_n(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, cudaStream_t st) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    TRB_CUDA_CHECK(cudaGetDevice(&dev));
+    if (!attr_set[dev & 63]) {
+        TRB_CUDA_CHECK(cudaFuncSetAttribute(decode_tc_kernel<NROW>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM));
+        attr_set[dev & 63] = true;
+    }
+    dim3 grid(p.nsplit, p.hkv);
+    TRB_CUDA_CHECK(launch_kernel(decode_tc_kernel<NROW>, grid, dim3(8 * NROW + 64), (size_t)TC_SMEM, st, true, mk, mv, p));
+    return TRB_OK;
+}
+
+static int launch_decode_tc(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, cudaStream_t st) {
+    if (p.rows <= 16) return launch_decode_tc_n<16>(mk, mv, p, st);
+    if (p.rows <= 32) return launch_decode_tc_n<32>(mk, mv, p, st);
+    return launch_decode_tc_n<48>(mk, mv, p, st);
+}
+
 }  // namespace trb
 
 using namespace trb;
+
+extern "C" int trb_set_decode_tensor_rows(int32_t min_rows) {
+    g_tc_min_rows = min_rows > 0 ? min_rows : DEC_TC_DEFAULT_MIN_ROWS;
+    return TRB_OK;
+}
 
 extern "C" size_t trb_decode_workspace_bytes(int32_t hq, int32_t hkv, int32_t d, int32_t m) {
     if (hq < 1 || hkv < 1 || hq % hkv || m < 1) return 0;
@@ -899,9 +945,14 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
 
     const int row_bytes = c.d * (c.fp8 ? 1 : 2);
     CUtensorMap mk, mv;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (c.fp8 && c.d == TC_D && c.ring == 0 && a->window == 0 && rows >= g_tc_min_rows) {
+        if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, row_bytes, TC_BN, &mk))) return rc;
+        if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, row_bytes, TC_BN, &mv))) return rc;
+        return launch_decode_tc(mk, mv, p, st);
+    }
     if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, row_bytes, DEC_BN, &mk))) return rc;
     if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, row_bytes, DEC_BN, &mv))) return rc;
-    cudaStream_t st = (cudaStream_t)stream;
     if (c.d == 256) return c.fp8 ? launch_decode<256, true>(mk, mv, p, st) : launch_decode<256, false>(mk, mv, p, st);
     return c.fp8 ? launch_decode<128, true>(mk, mv, p, st) : launch_decode<128, false>(mk, mv, p, st);
 }

@@ -1,0 +1,466 @@
+// Split-K flash-decoding for several query rows per kv head (speculative verify, M >= 2) on the
+// 5th-generation tensor cores.  Included by decode.cu after DecodeParams and decode_tail.
+//
+// With 6 M query rows per kv head, converting every e4m3 tile to f16 once per 8-row slice (the
+// mma.sync kernel) costs more issue slots than the stream leaves; tcgen05.mma reads the e4m3
+// codes of the cache straight from the TMA tile.  The products are laid out transposed, so
+// that the 128-row operand is always the cache tile and the few query rows are the N extent:
+//     S^T[128 keys x 2N]  = K . [Qhi ; Qlo]^T      A = K tile (K-major),  B = stacked query block
+//     O^T[128 dims x 2N] += V^T . [Phi ; Plo]^T    A = V tile (MN-major), B = stacked probabilities
+// (two O^T accumulators for the 256 dims).  hi + lo are two e4m3 terms of a value (8 significant
+// bits, what bf16 carries); stacking them as 2N operand rows reads each cache tile once per
+// product, and the two partial results are added after the tensor-memory load.
+//
+// Warp roles: one softmax warpgroup per 16 query rows (thread = key of the tile = TMEM lane of
+// S^T; for the O^T correction and the epilogue the same thread = head dim), then one TMA
+// producer warp and one MMA issuer warp: 192, 320 or 448 threads for up to 16, 32, 48 rows.  The
+// warpgroups work independently on their rows (own named barrier, own statistics), so the work
+// per thread does not grow with M.  S^T and P are double-buffered.  Row maxima over the keys of
+// a tile are warp reductions (redux.sync.max.f32) followed by a 4-warp exchange through shared
+// memory; an O^T column is rescaled only when its row maximum moved.  The CTA's result goes to the split workspace in the layout of decode_kernel, and the
+// same ticket + tail finishes the launch.  Every wait is bounded.
+#pragma once
+#include "tc.cuh"
+
+namespace trb {
+
+constexpr int TC_BN = 128;                     // keys per tile = M of every MMA
+constexpr int TC_D = 256;
+constexpr int TC_MAX_THREADS = 448;           // 4 softmax warps per 16 query rows + TMA warp + MMA warp
+constexpr int TC_KSLOTS = 3, TC_VSLOTS = 2;
+constexpr int TC_TILE = TC_BN * TC_D;          // 32 KB of e4m3 codes
+constexpr int TC_MAX_N2 = 96;                  // stacked rows: 2 x (query rows rounded up to 16)
+constexpr int TC_OFF_K = 0;
+constexpr int TC_OFF_V = TC_OFF_K + TC_KSLOTS * TC_TILE;
+constexpr int TC_OFF_Q = TC_OFF_V + TC_VSLOTS * TC_TILE;          // [2 column blocks][2N rows][128 B]
+constexpr int TC_Q_BYTES = 2 * TC_MAX_N2 * 128;
+constexpr int TC_OFF_P = TC_OFF_Q + TC_Q_BYTES;                    // 2 buffers of [2N rows][128 B]
+constexpr int TC_P_BYTES = TC_MAX_N2 * 128;
+constexpr int TC_OFF_SC = TC_OFF_P + 2 * TC_P_BYTES;               // [KSLOTS][2][128] floats
+constexpr int TC_OFF_ST = TC_OFF_SC + TC_KSLOTS * 2 * TC_BN * 4;   // per-row statistics, see below
+constexpr int TC_ST_FLOATS = 4 * 48 + 4 * 48 + 8;
+constexpr int TC_OFF_BAR = TC_OFF_ST + TC_ST_FLOATS * 4;
+constexpr int TC_SMEM = TC_OFF_BAR + 256 + 1024;
+constexpr int TC_TMEM_COLS = 512;
+constexpr int TC_TMEM_S = 0;                   // S^T buffers at columns 0 and 128
+constexpr int TC_TMEM_O = 256;                 // O^T accumulators (dims 0-127, 128-255) at columns 256 and 384
+
+__device__ __forceinline__ float redux_max(float v) {
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, float (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]), "=f"(v[9]),
+          "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ float tmem_ld1(uint32_t taddr) {
+    uint32_t r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, float v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(__float_as_uint(v)) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int NROW>
+__global__ void __launch_bounds__(8 * NROW + 64, 1)
+decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
+    constexpr int D = TC_D, N2 = 2 * NROW, NCH = NROW / 16;
+    constexpr int NTHREADS = 8 * NROW + 64, W_TMA = 4 * NCH, W_MMA = 4 * NCH + 1;
+    extern __shared__ uint8_t tc_smem_raw[];
+    uint8_t *smem = tc_smem_raw + ((1024u - (smem_u32(tc_smem_raw) & 1023u)) & 1023u);
+    float *sm_sc = reinterpret_cast<float *>(smem + TC_OFF_SC);
+    float *sm_wmax = reinterpret_cast<float *>(smem + TC_OFF_ST);        // [4][48] warp maxima / warp sums
+    float *sm_mnew = sm_wmax + 4 * 48;                                    // [48] running row maxima
+    float *sm_alpha = sm_mnew + 48;                                       // [48] factor of the rows whose maximum moved
+    float *sm_qinv = sm_alpha + 48;                                       // [48] inverse of the query row scale
+    int *sm_hi = reinterpret_cast<int *>(sm_qinv + 48);                   // [48] last visible key of a row
+    uint32_t *sm_moved = reinterpret_cast<uint32_t *>(sm_hi + 48);        // [2] bit masks of moved rows
+    int *sm_flag = reinterpret_cast<int *>(sm_moved + 2);                 // [3] used by decode_tail
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm_flag + 3);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TC_OFF_BAR);
+    uint64_t *k_full = bars, *k_free = bars + 3, *v_full = bars + 6, *v_free = bars + 8;
+    uint64_t *s_full = bars + 10, *s_free = bars + 12, *p_full = bars + 14, *pv_done = bars + 16;
+
+    const int split = blockIdx.x, j = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+
+    // ---- ranges, all derived from the device cursor (as in decode_kernel, in 128-key tiles) ----
+    const long long pos = load_cursor(p.pos);
+    const long long live = pos + (p.new_rows ? p.m : 0);
+    long long lloc = live - p.shard_lo;
+    if (lloc < 0) lloc = 0;
+    if (lloc > p.max_len) {
+        if (!p.sharded && tid == 0 && split == 0 && j == 0) raise_status(TRB_ST_CURSOR_RANGE);
+        lloc = p.max_len;
+    }
+    const int n_tiles = (int)((lloc + TC_BN - 1) / TC_BN);
+    int per = (n_tiles + p.nsplit - 1) / p.nsplit;
+    if (per < 1) per = 1;
+    int active = (n_tiles + per - 1) / per;
+    if (active < 1) active = 1;
+    if (split >= active) return;
+    const int t0 = split * per;
+    int my_tiles = (t0 + per < n_tiles ? t0 + per : n_tiles) - t0;
+    if (my_tiles < 0) my_tiles = 0;
+    const int lloc_i = (int)lloc;
+    const int pos_loc = (int)(pos - p.shard_lo);
+
+    if (tid == 0) {
+        for (int s = 0; s < TC_KSLOTS; ++s) { mbar_init(&k_full[s], 33u); mbar_init(&k_free[s], 1u + 4u * NCH); }
+        for (int s = 0; s < TC_VSLOTS; ++s) { mbar_init(&v_full[s], 1u); mbar_init(&v_free[s], 1u); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1u); mbar_init(&s_free[b], 4u * NCH); mbar_init(&p_full[b], 4u * NCH); mbar_init(&pv_done[b], 1u); }
+        mbar_fence_init();
+        tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
+    }
+    if (warp == 0) { tmem_alloc(tmem_slot, TC_TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // producer helpers (the TMA warp)
+    auto issue_k = [&](int i) {
+        const int s = i % TC_KSLOTS;
+        const int row0 = (t0 + i) * TC_BN;
+        uint8_t *kt = smem + TC_OFF_K + s * TC_TILE;
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&k_full[s], TC_TILE);
+            tma_load_4d(kt, &tm_k, &k_full[s], 0, 0, row0, j);
+            tma_load_4d(kt + TC_BN * 128, &tm_k, &k_full[s], 0, 1, row0, j);
+        }
+#pragma unroll
+        for (int hh = 0; hh < 4; ++hh) {
+            const long long r = (long long)row0 + lane + 32 * hh;
+            const bool ok = r < p.max_len;
+            const long long off = (long long)j * p.max_len + (ok ? r : 0);
+            cp_async_4(&sm_sc[(s * 2 + 0) * TC_BN + lane + 32 * hh], p.ks + off, ok ? 4u : 0u);
+            cp_async_4(&sm_sc[(s * 2 + 1) * TC_BN + lane + 32 * hh], p.vs + off, ok ? 4u : 0u);
+        }
+        cp_async_mbar_arrive_noinc(&k_full[s]);
+    };
+    auto issue_v = [&](int i) {
+        const int s = i % TC_VSLOTS;
+        const int row0 = (t0 + i) * TC_BN;
+        uint8_t *vt = smem + TC_OFF_V + s * TC_TILE;
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&v_full[s], TC_TILE);
+            tma_load_4d(vt, &tm_v, &v_full[s], 0, 0, row0, j);
+            tma_load_4d(vt + TC_BN * 128, &tm_v, &v_full[s], 0, 1, row0, j);
+        }
+    };
+    // Tiles below the rows that the preceding append writes depend on nothing in flight: the first
+    // two of them are requested before the dependency wait.
+    const long long fresh_from = p.new_rows ? pos - p.shard_lo : (1LL << 62);
+    int pre = 0;
+    if (warp == W_TMA)
+        while (pre < my_tiles && pre < 2 && (long long)(t0 + pre + 1) * TC_BN <= fresh_from) { issue_k(pre); issue_v(pre); ++pre; }
+    pdl_wait();
+    pdl_launch_dependents();
+    const unsigned int epoch = tid == 0 ? *(volatile unsigned int *)&p.counters[128 + j] : 0u;
+
+    // ---- query block: rows r of this kv head (query r / g, head j g + r % g) as two stacked e4m3
+    // copies with a power-of-two row scale; thread = (row, 64-dim quarter)
+    {
+        const int row = tid >> 2, quarter = tid & 3;
+        const bool in_block = row < NROW, valid = row < p.rows && in_block;
+        const int qi = valid ? row / p.g : 0, hq = valid ? j * p.g + row % p.g : 0;
+        const __nv_bfloat16 *qp = p.q + ((long long)qi * p.hq + hq) * D + quarter * 64;
+        uint4 raw[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) raw[c] = valid ? __ldg(reinterpret_cast<const uint4 *>(qp) + c) : make_uint4(0u, 0u, 0u, 0u);
+        float amax = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[c]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(b2[e]); amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y))); }
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;
+        if (amax == 0.f || e < -90 || !valid) e = 7;
+        if (e > 90) e = 90;
+        const float sc = valid ? __uint_as_float((uint32_t)(127 + 7 - e) << 23) : 0.f;
+        if (in_block) {
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {                                  // 16 dims per chunk
+                const int c = quarter * 4 + cc;
+                uint32_t hw[4], lw[4];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const uint32_t *rw = reinterpret_cast<const uint32_t *>(&raw[2 * cc + (w >> 1)]) + 2 * (w & 1);
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(rw));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(rw + 1));
+                    const float y[4] = {a.x * sc, a.y * sc, b.x * sc, b.y * sc};
+                    pf_split4(y, hw[w], lw[w]);
+                }
+                const uint32_t off = (c >> 3) * (N2 * 128) + sw128(row, (c & 7) * 16);
+                *reinterpret_cast<uint4 *>(smem + TC_OFF_Q + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                *reinterpret_cast<uint4 *>(smem + TC_OFF_Q + off + NROW * 128) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            }
+            if (quarter == 0) {
+                sm_qinv[row] = __uint_as_float((uint32_t)(127 - 7 + e) << 23);
+                int hi = lloc_i - 1;
+                if (p.new_rows && pos_loc + qi < hi) hi = pos_loc + qi;
+                sm_hi[row] = hi;
+                sm_mnew[row] = -INFINITY;
+            }
+        }
+    }
+    fence_async_smem();
+    __syncthreads();
+
+    bool ok = true;
+    if (warp == W_TMA) {
+        // ================================ TMA producer ================================
+        for (int i = pre; i < my_tiles; ++i) {
+            if (i >= TC_KSLOTS && !mbar_wait(&k_free[i % TC_KSLOTS], ((i / TC_KSLOTS) & 1) ^ 1)) break;
+            issue_k(i);
+            if (i >= TC_VSLOTS && !mbar_wait(&v_free[i % TC_VSLOTS], ((i / TC_VSLOTS) & 1) ^ 1)) break;
+            issue_v(i);
+        }
+    } else if (warp == W_MMA) {
+        // ================================ MMA issuer ==================================
+        // order on the tensor pipe: QK(0), QK(1), PV(0), QK(2), PV(1), ...
+        const uint32_t q_sm = smem_u32(smem + TC_OFF_Q), p_sm = smem_u32(smem + TC_OFF_P);
+        constexpr uint32_t IDESC_QK = umma_idesc_f8(TC_BN, N2, false, false), IDESC_PV = umma_idesc_f8(128, N2, true, false);
+        auto issue_qk = [&](int i) -> bool {
+            const int s = i % TC_KSLOTS, b = i & 1;
+            if (!mbar_wait(&k_full[s], (i / TC_KSLOTS) & 1)) return false;
+            if (i >= 2 && !mbar_wait(&s_free[b], ((i >> 1) & 1) ^ 1)) return false;      // S^T of tile i-2 has been read
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t kt = smem_u32(smem + TC_OFF_K + s * TC_TILE);
+#pragma unroll
+                for (int sg = 0; sg < 2; ++sg)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t a = umma_desc(kt + sg * (TC_BN * 128) + k * 32, 16, 1024);
+                        const uint64_t bd = umma_desc(q_sm + sg * (N2 * 128) + k * 32, 16, 1024);
+                        tc_mma_f8(tmem + TC_TMEM_S + b * 128, a, bd, IDESC_QK, (sg | k) ? 1u : 0u);
+                    }
+                tc_commit(&s_full[b]);
+                tc_commit(&k_free[s]);
+            }
+            __syncwarp();
+            return true;
+        };
+        if (my_tiles > 0) ok = issue_qk(0);
+        for (int i = 0; i < my_tiles && ok; ++i) {
+            const int b = i & 1;
+            if (i + 1 < my_tiles && !(ok = issue_qk(i + 1))) break;
+            if (!(ok = mbar_wait(&p_full[b], (i >> 1) & 1))) break;                       // P of tile i staged, O^T corrected
+            if (!(ok = mbar_wait(&v_full[b], (i >> 1) & 1))) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t vt = smem_u32(smem + TC_OFF_V + b * TC_TILE), pb = p_sm + b * TC_P_BYTES;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t a = umma_desc(vt + h * (TC_BN * 128) + k * (32 * 128), TC_BN * 128, 1024);
+                        const uint64_t bd = umma_desc(pb + k * 32, 16, 1024);
+                        tc_mma_f8(tmem + TC_TMEM_O + h * 128, a, bd, IDESC_PV, (i | k) ? 1u : 0u);
+                    }
+                tc_commit(&v_free[b]);
+                tc_commit(&pv_done[b]);
+            }
+            __syncwarp();
+        }
+    } else if (warp < 4 * NCH) {
+        // ====== softmax / correction / epilogue: one warpgroup per 16 query rows; thread = key lane = dim lane ======
+        const int rg = warp >> 2, qw = warp & 3;                               // row group, lane quarter
+        const int kl = qw * 32 + lane;                                         // 0..127
+        const int r0 = rg * 16;                                                // first row of this group
+        const uint32_t lane_addr = tmem + ((uint32_t)(qw * 32) << 16);
+        const uint32_t p_chunk = (uint32_t)(kl >> 4), p_byte = (uint32_t)(kl & 15);
+        const int all_hi = p.new_rows ? (pos_loc < lloc_i - 1 ? pos_loc : lloc_i - 1) : lloc_i - 1;
+        float *g_wmax = sm_wmax + rg * 64;                                     // [4 quarters][16 rows]
+        float *g_mnew = sm_mnew + r0, *g_alpha = sm_alpha + r0;
+        const float *g_qinv = sm_qinv + r0;
+        const int *g_hi = sm_hi + r0;
+        const int bar_id = 1 + rg;
+        float lsum[16];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) lsum[r] = 0.f;
+        float m_own = -INFINITY;                                               // threads kl < 16: running maximum of row r0 + kl
+
+        for (int i = 0; i < my_tiles && ok; ++i) {
+            const int s = i % TC_KSLOTS, b = i & 1;
+            const int kv = (t0 + i) * TC_BN + kl;                              // virtual row of this thread's key
+            if (!(ok = mbar_wait(&k_full[s], (i / TC_KSLOTS) & 1))) break;
+            const float ksc = sm_sc[(s * 2 + 0) * TC_BN + kl], vsc = sm_sc[(s * 2 + 1) * TC_BN + kl];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&k_free[s]);                            // the scale slot may be refilled
+            const bool key_ok = kv < lloc_i && vsc > 0.f;
+            const float kfac = ksc * p.scale_log2;
+            const float vlog = key_ok ? __log2f(vsc) : 0.f;
+            const float vinv = key_ok ? __fdividef(0.00390625f, vsc) : 0.f;     // 1 / (256 v_scale)
+            if (!(ok = mbar_wait(&s_full[b], (i >> 1) & 1))) break;
+            tc_fence_after();
+            float tv[16];
+            {
+                float hi[16], lo[16];
+                tmem_ld16_nowait(lane_addr + TC_TMEM_S + b * 128 + r0, hi);
+                tmem_ld16_nowait(lane_addr + TC_TMEM_S + b * 128 + NROW + r0, lo);
+                tmem_wait_ld();
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const float4 qv = *reinterpret_cast<const float4 *>(&g_qinv[q4 * 4]);
+                    tv[q4 * 4 + 0] = fmaf((hi[q4 * 4 + 0] + lo[q4 * 4 + 0]) * kfac, qv.x, vlog);
+                    tv[q4 * 4 + 1] = fmaf((hi[q4 * 4 + 1] + lo[q4 * 4 + 1]) * kfac, qv.y, vlog);
+                    tv[q4 * 4 + 2] = fmaf((hi[q4 * 4 + 2] + lo[q4 * 4 + 2]) * kfac, qv.z, vlog);
+                    tv[q4 * 4 + 3] = fmaf((hi[q4 * 4 + 3] + lo[q4 * 4 + 3]) * kfac, qv.w, vlog);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free[b]);                            // tile i+2 may overwrite this buffer
+            if (!((t0 + i) * TC_BN + TC_BN - 1 <= all_hi)) {                   // the tiles at the end of the live range
+#pragma unroll
+                for (int r = 0; r < 16; ++r)
+                    if (!(key_ok && kv <= g_hi[r])) tv[r] = -INFINITY;
+            }
+            // ---- row maxima over the 128 keys: warp reduction, then the four warps through shared memory
+            {
+                float wm[16];
+#pragma unroll
+                for (int r = 0; r < 16; ++r) wm[r] = redux_max(tv[r]);
+                if (lane == 0) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        *reinterpret_cast<float4 *>(&g_wmax[qw * 16 + q4 * 4]) = make_float4(wm[q4 * 4], wm[q4 * 4 + 1], wm[q4 * 4 + 2], wm[q4 * 4 + 3]);
+                }
+            }
+            named_barrier(bar_id, 128);
+            if (qw == 0) {                                                     // one thread per row
+                bool moved = false;
+                if (lane < 16) {
+                    const float mt = fmaxf(fmaxf(g_wmax[lane], g_wmax[16 + lane]), fmaxf(g_wmax[32 + lane], g_wmax[48 + lane]));
+                    const float mn = fmaxf(m_own, mt);
+                    moved = mn != m_own && i > 0;
+                    g_alpha[lane] = mn == -INFINITY ? 1.f : fast_exp2(m_own - mn);
+                    g_mnew[lane] = mn;
+                    m_own = mn;
+                }
+                const uint32_t mask = __ballot_sync(0xffffffffu, moved);
+                if (lane == 0) sm_moved[rg] = mask;
+            }
+            named_barrier(bar_id, 128);
+            uint32_t mk = sm_moved[rg];
+            // the P buffer of tile i-2 must have been consumed; a correction needs PV(i-1) complete
+            if (i >= 2 && !(ok = mbar_wait(&pv_done[b], ((i >> 1) & 1) ^ 1))) break;
+            if (mk) {
+                if (!(ok = mbar_wait(&pv_done[b ^ 1], ((i - 1) >> 1) & 1))) break;
+                tc_fence_after();
+                while (mk) {
+                    const int rr = __ffs(mk) - 1;
+                    mk &= mk - 1;
+                    const float al = g_alpha[rr];
+                    const uint32_t a0 = lane_addr + TC_TMEM_O + r0 + rr, a1 = a0 + NROW, a2 = a0 + 128, a3 = a2 + NROW;
+                    float o0 = tmem_ld1(a0), o1 = tmem_ld1(a1), o2 = tmem_ld1(a2), o3 = tmem_ld1(a3);
+                    tmem_wait_ld();
+                    tmem_st1(a0, o0 * al); tmem_st1(a1, o1 * al); tmem_st1(a2, o2 * al); tmem_st1(a3, o3 * al);
+                }
+                tmem_wait_st();
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const float4 al = *reinterpret_cast<const float4 *>(&g_alpha[q4 * 4]);
+                    lsum[q4 * 4 + 0] *= al.x; lsum[q4 * 4 + 1] *= al.y; lsum[q4 * 4 + 2] *= al.z; lsum[q4 * 4 + 3] *= al.w;
+                }
+            }
+            // ---- probabilities (x 256) as hi + lo e4m3 codes, one byte per (row, key): rows of 128 keys
+            uint8_t *pb = smem + TC_OFF_P + b * TC_P_BYTES + r0 * 128;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const float4 mn = *reinterpret_cast<const float4 *>(&g_mnew[q4 * 4]);
+                const float ms[4] = {mn.x == -INFINITY ? 0.f : mn.x, mn.y == -INFINITY ? 0.f : mn.y,
+                                     mn.z == -INFINITY ? 0.f : mn.z, mn.w == -INFINITY ? 0.f : mn.w};
+#pragma unroll
+                for (int h2 = 0; h2 < 2; ++h2) {
+                    const int r = q4 * 4 + 2 * h2;
+                    const float p0 = fast_exp2(tv[r] - ms[2 * h2] + 8.f), p1 = fast_exp2(tv[r + 1] - ms[2 * h2 + 1] + 8.f);
+                    uint32_t hc, lc;
+                    const float2 pq = pf_split2_hq(p0, p1, hc, lc);            // the weights as the MMA sees them
+                    lsum[r] = fmaf(pq.x, vinv, lsum[r]);
+                    lsum[r + 1] = fmaf(pq.y, vinv, lsum[r + 1]);
+                    uint8_t *d0 = pb + r * 128 + (((p_chunk ^ (uint32_t)(r & 7)) << 4) | p_byte);
+                    uint8_t *d1 = pb + (r + 1) * 128 + (((p_chunk ^ (uint32_t)((r + 1) & 7)) << 4) | p_byte);
+                    d0[0] = (uint8_t)(hc & 0xffu); d1[0] = (uint8_t)(hc >> 8);
+                    d0[NROW * 128] = (uint8_t)(lc & 0xffu); d1[NROW * 128] = (uint8_t)(lc >> 8);
+                }
+            }
+            fence_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[b]);
+        }
+        // ---- epilogue: this CTA's partial rows.  acc[row][dim] = (hi + lo part of O^T[dim][row]) / 256
+        if (ok && my_tiles > 0) ok = mbar_wait(&pv_done[(my_tiles - 1) & 1], ((my_tiles - 1) >> 1) & 1);
+        tc_fence_after();
+        const long long part_base = ((long long)j * p.nsplit + split) * p.rows_pad;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+            float hi[16], lo[16];
+            if (my_tiles > 0) {
+                tmem_ld16_nowait(lane_addr + TC_TMEM_O + h * 128 + r0, hi);
+                tmem_ld16_nowait(lane_addr + TC_TMEM_O + h * 128 + NROW + r0, lo);
+                tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) hi[e] = lo[e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const int r = r0 + e;
+                if (r < p.rows) p.part_acc[(part_base + r) * D + h * 128 + kl] = (hi[e] + lo[e]) * 0.00390625f;
+            }
+        }
+        tc_fence_before();
+        // row sums over the 128 key lanes
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            float v = lsum[r];
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            lsum[r] = v;
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4)
+                *reinterpret_cast<float4 *>(&g_wmax[qw * 16 + q4 * 4]) = make_float4(lsum[q4 * 4], lsum[q4 * 4 + 1], lsum[q4 * 4 + 2], lsum[q4 * 4 + 3]);
+        }
+        named_barrier(bar_id, 128);
+        if (kl < 16 && r0 + kl < p.rows) {
+            const float l = (g_wmax[kl] + g_wmax[16 + kl]) + (g_wmax[32 + kl] + g_wmax[48 + kl]);
+            p.part_ml[(part_base + r0 + kl) * 2 + 0] = m_own;
+            p.part_ml[(part_base + r0 + kl) * 2 + 1] = l;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TC_TMEM_COLS); }
+    decode_tail<D, NTHREADS>(p, smem, sm_flag, j, active, epoch);
+}
+
+}  // namespace trb

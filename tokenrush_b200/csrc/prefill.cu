@@ -17,6 +17,7 @@
 // producer, warp 9 MMA issuer.  S is double-buffered in tensor memory, so QK of tile i+1 runs
 // on the tensor pipe while tile i is in softmax.  Every wait is bounded.
 #include "common.cuh"
+#include "tc.cuh"
 #include "tmap.h"
 
 namespace trb {
@@ -50,101 +51,6 @@ struct PrefillParams {
     long long pos, max_len;
     float scale_log2;
 };
-
-// ---- tcgen05 wrappers -------------------------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
-          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
-          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
-          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
-          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
-          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-        : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-// UMMA shared-memory descriptor, 128-byte swizzle, version 1 (sm_100).
-// K-major:  rows of 128 bytes, 8-row atoms SBO apart.  MN-major: 128-byte chunks of the MN
-// extent LBO apart, 8-row (K) atoms SBO apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= (uint64_t)1 << 46;          // descriptor version
-    d |= (uint64_t)2 << 61;          // SWIZZLE_128B
-    return d;
-}
-// instruction descriptor: fp32 accumulate, e4m3 x e4m3, M = 128
-__host__ __device__ constexpr uint32_t umma_idesc_f8(int n, bool b_mn_major) {
-    return (1u << 4) | (0u << 7) | (0u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(PF_BM >> 4) << 24);
-}
-
-// four fp32 -> (hi codes, lo codes) as in hi + lo ~= x
-__device__ __forceinline__ void pf_split4(const float (&x)[4], uint32_t &hi, uint32_t &lo) {
-    const __nv_fp8x2_storage_t h01 = __nv_cvt_float2_to_fp8x2(make_float2(x[0], x[1]), __NV_SATFINITE, __NV_E4M3);
-    const __nv_fp8x2_storage_t h23 = __nv_cvt_float2_to_fp8x2(make_float2(x[2], x[3]), __NV_SATFINITE, __NV_E4M3);
-    const float2 f01 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(h01, __NV_E4M3)));
-    const float2 f23 = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(h23, __NV_E4M3)));
-    const __nv_fp8x2_storage_t l01 = __nv_cvt_float2_to_fp8x2(make_float2(x[0] - f01.x, x[1] - f01.y), __NV_SATFINITE, __NV_E4M3);
-    const __nv_fp8x2_storage_t l23 = __nv_cvt_float2_to_fp8x2(make_float2(x[2] - f23.x, x[3] - f23.y), __NV_SATFINITE, __NV_E4M3);
-    hi = (uint32_t)h01 | ((uint32_t)h23 << 16);
-    lo = (uint32_t)l01 | ((uint32_t)l23 << 16);
-}
-
-// two non-negative fp32 values (<= 256) -> 16 bits of hi codes and 16 bits of lo codes, through
-// packed f16 arithmetic (f16 holds x to 11 bits, hi + lo keep 8 of them)
-__device__ __forceinline__ void pf_split2_h(float x0, float x1, uint32_t &hi, uint32_t &lo) {
-    const __half2 x = __floats2half2_rn(x0, x1);
-    const __nv_fp8x2_storage_t h = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw *>(&x), __NV_SATFINITE, __NV_E4M3);
-    const __half2 hb = __half2(__nv_cvt_fp8x2_to_halfraw2(h, __NV_E4M3));
-    const __half2 r = __hsub2(x, hb);
-    const __nv_fp8x2_storage_t l = __nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<const __half2_raw *>(&r), __NV_SATFINITE, __NV_E4M3);
-    hi = h; lo = l;
-}
-
-// byte offset of (row, byte) in a [rows][128 B] block with the 128-byte swizzle
-__device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t byte) {
-    return row * 128u + ((((byte >> 4) ^ (row & 7u)) & 7u) << 4) + (byte & 15u);
-}
 
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -210,7 +116,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         // that QK(i+1) runs while the softmax warps work on tile i.
         const uint32_t q_hi = smem_u32(smem + PF_OFF_Q), q_lo = q_hi + PF_Q_BYTES;
         const uint32_t p_sm = smem_u32(smem + PF_OFF_P);
-        constexpr uint32_t IDESC_QK = umma_idesc_f8(PF_BN, false), IDESC_PV = umma_idesc_f8(PF_D, true);
+        constexpr uint32_t IDESC_QK = umma_idesc_f8(PF_BM, PF_BN, false, false), IDESC_PV = umma_idesc_f8(PF_BM, PF_D, false, true);
         auto issue_qk = [&](int i) -> bool {
             const int s = i % PF_STAGES, b = i & 1;
             const uint32_t kt = smem_u32(smem + PF_OFF_KV + s * 2 * PF_TILE);
