@@ -109,7 +109,7 @@ __device__ __forceinline__ int acc_dim(int a, int i, int g) {
 
 // Ticket and tail shared by the decode kernels.  Called by every thread of the CTA once the
 // CTA's partial (max, sum, acc) rows are written to the workspace.  `smem` is scratch from its
-// start (at least 6 KB), `sm_flag` three ints outside that scratch.
+// start (at least 16 KB), `sm_flag` three ints outside that scratch.
 template <int D, int NTHREADS>
 __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem, int *sm_flag, const int j, const int active,
                                             const unsigned int epoch) {
@@ -119,6 +119,8 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
     // and merges them, so the combine runs on many SMs.  The last CTA keeps claiming until no
     // row is left, so the result is complete even if every helper gave up waiting.
     unsigned int *ticket = p.counters + j, *claim = p.counters + 64 + j, *seq = p.counters + 128 + j;
+    constexpr int ITEMS = D / 4, GROUPS = NTHREADS / ITEMS;
+    const int rc = (p.rows > active && p.p2p_world == 0 && GROUPS >= 2) ? 2 : 1;     // rows per claim, see below
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -131,9 +133,9 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
             *(volatile unsigned int *)seq = epoch + 1u;
         } else {
             state = 0;
-            // only the last `rows` arrivals can find a row to merge; earlier ones leave at once and
-            // free their SM for the next kernel in the stream
-            for (int it = 0; it < 4096 && (int)old >= active - p.rows; ++it) {
+            // only the last arrivals (one per claim; a claim is one or two rows) can find a row to merge;
+            // earlier ones leave at once and free their SM for the next kernel in the stream
+            for (int it = 0; it < 4096 && (int)old >= active - (p.rows + rc - 1) / rc; ++it) {
                 if (*(volatile unsigned int *)seq == epoch + 1u) { state = 1; break; }
                 __nanosleep(100);
             }
@@ -145,72 +147,83 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
     if (*sm_flag == 0) return;                                          // gave up waiting: the others finish the rows
     __threadfence();
 
-    // 3. tail: LSE merge of one output row per claim over the active splits (+ extra partials), in
-    // split order: thread (item, group) sums the splits of its group, the groups are added in
-    // group order through shared memory.
+    // 3. tail: LSE merge of the output rows over the active splits (+ extra partials), in split
+    // order: thread (item, group) sums the splits of its group, the groups are added in group
+    // order through shared memory.  With more rows than splits (M-row verify) a claim takes two
+    // rows and the thread groups form two teams, one per row, so that one round of claims covers
+    // all rows.
     const int n_parts = active + p.n_extra;
-    constexpr int ITEMS = D / 4, GROUPS = NTHREADS / ITEMS;
-    float *sm_m = reinterpret_cast<float *>(smem);                      // [n_parts]
-    float *sm_l = sm_m + (DEC_MAX_SPLITS + 4);                          // [n_parts]
-    float4 *sm_red = reinterpret_cast<float4 *>(sm_l + (DEC_MAX_SPLITS + 4));   // [GROUPS][ITEMS]
-    int *sm_claim = sm_flag + 1;
+    const int gt = GROUPS / rc;                                         // groups per team
     const int item = tid % ITEMS, grp = tid / ITEMS, d4 = item * 4;
+    const int team = grp / gt, tgrp = grp - team * gt;                 // team >= rc: idle threads
+    const int ttid = tid - team * gt * ITEMS, team_threads = gt * ITEMS;
+    const bool in_team = team < rc;
+    float *sm_m = reinterpret_cast<float *>(smem) + (in_team ? team : 0) * 2 * (DEC_MAX_SPLITS + 4);   // [n_parts] per team
+    float *sm_l = sm_m + (DEC_MAX_SPLITS + 4);                          // [n_parts]
+    float4 *sm_red = reinterpret_cast<float4 *>(reinterpret_cast<float *>(smem) + 4 * (DEC_MAX_SPLITS + 4)) +
+                     (in_team ? team : 0) * gt * ITEMS;                 // [gt][ITEMS] per team
+    int *sm_claim = sm_flag + 1;
     for (;;) {
         __syncthreads();
         if (tid == 0) *sm_claim = (int)atomicAdd(claim, 1u);
         __syncthreads();
-        const int row = *sm_claim;
-        if (row >= p.rows) break;
-        const int qi = row / p.g, hq = j * p.g + row % p.g;
+        if (*sm_claim * rc >= p.rows) break;
+        const int row = *sm_claim * rc + team;
+        const bool row_on = in_team && row < p.rows;
+        const int qi = row_on ? row / p.g : 0, hq = row_on ? j * p.g + row % p.g : 0;
         const long long grow = (long long)qi * p.hq + hq;
-        // one round trip: the (max, sum) pairs of all splits and this thread's first eight slices of
-        // the accumulators are requested together; the weights are applied once both are here
-        const float *pa = p.part_acc + ((long long)j * p.nsplit * p.rows_pad + row) * D + d4;
+        // one round trip: the (max, sum) pairs of all splits and this thread's first slices of the
+        // accumulators are requested together; the weights are applied once both are here
+        const float *pa = p.part_acc + ((long long)j * p.nsplit * p.rows_pad + (row_on ? row : 0)) * D + d4;
         const long long pstride = (long long)p.rows_pad * D;
-        float4 pre[8];
+        constexpr int PRE = 13;
+        float4 pre[PRE];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int sp = grp + u * GROUPS;
-            pre[u] = sp < active ? __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int u = 0; u < PRE; ++u) {
+            const int sp = tgrp + u * gt;
+            pre[u] = (row_on && sp < active) ? __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        for (int sp = tid; sp < n_parts; sp += NTHREADS) {
-            float2 v;
-            if (sp < active) v = __ldcg(reinterpret_cast<const float2 *>(&p.part_ml[(((long long)j * p.nsplit + sp) * p.rows_pad + row) * 2]));
-            else v = *reinterpret_cast<const float2 *>(&p.extra_ml[(grow * p.n_extra + (sp - active)) * 2]);
-            sm_m[sp] = v.x; sm_l[sp] = v.y;
-        }
+        if (row_on)
+            for (int sp = ttid; sp < n_parts; sp += team_threads) {
+                float2 v;
+                if (sp < active) v = __ldcg(reinterpret_cast<const float2 *>(&p.part_ml[(((long long)j * p.nsplit + sp) * p.rows_pad + row) * 2]));
+                else v = *reinterpret_cast<const float2 *>(&p.extra_ml[(grow * p.n_extra + (sp - active)) * 2]);
+                sm_m[sp] = v.x; sm_l[sp] = v.y;
+            }
         __syncthreads();
         float mmax = -INFINITY, lsum = 0.f;
-        for (int sp = lane; sp < n_parts; sp += 32) mmax = fmaxf(mmax, sm_m[sp]);
-        mmax = warp_max(mmax);
-        for (int sp = lane; sp < n_parts; sp += 32) lsum += sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax) * sm_l[sp];
-        lsum = warp_sum(lsum);
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row_on) {
+            for (int sp = lane; sp < n_parts; sp += 32) mmax = fmaxf(mmax, sm_m[sp]);
+            mmax = warp_max(mmax);
+            for (int sp = lane; sp < n_parts; sp += 32) lsum += sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax) * sm_l[sp];
+            lsum = warp_sum(lsum);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {                                      // split order within the group: ascending
-            const int sp = grp + u * GROUPS;
-            if (sp < active) {
-                const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
-                o.x = fmaf(w, pre[u].x, o.x); o.y = fmaf(w, pre[u].y, o.y); o.z = fmaf(w, pre[u].z, o.z); o.w = fmaf(w, pre[u].w, o.w);
+            for (int u = 0; u < PRE; ++u) {                                // split order within the group: ascending
+                const int sp = tgrp + u * gt;
+                if (sp < active) {
+                    const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
+                    o.x = fmaf(w, pre[u].x, o.x); o.y = fmaf(w, pre[u].y, o.y); o.z = fmaf(w, pre[u].z, o.z); o.w = fmaf(w, pre[u].w, o.w);
+                }
             }
-        }
 #pragma unroll 4
-        for (int sp = grp + 8 * GROUPS; sp < active; sp += GROUPS) {
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride));
-            const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
-            o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
-        }
-        if (grp == 0)
-            for (int e = 0; e < p.n_extra; ++e) {
-                const float4 v = *reinterpret_cast<const float4 *>(&p.extra_acc[(grow * p.n_extra + e) * D + d4]);
-                const float w = sm_m[active + e] == -INFINITY ? 0.f : fast_exp2(sm_m[active + e] - mmax);
+            for (int sp = tgrp + PRE * gt; sp < active; sp += gt) {
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride));
+                const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
                 o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
             }
-        sm_red[grp * ITEMS + item] = o;
+            if (tgrp == 0)
+                for (int e = 0; e < p.n_extra; ++e) {
+                    const float4 v = *reinterpret_cast<const float4 *>(&p.extra_acc[(grow * p.n_extra + e) * D + d4]);
+                    const float w = sm_m[active + e] == -INFINITY ? 0.f : fast_exp2(sm_m[active + e] - mmax);
+                    o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+                }
+            sm_red[tgrp * ITEMS + item] = o;
+        }
         __syncthreads();
-        const bool lead = grp == 0;                                      // these threads hold the row from here on
+        const bool lead = row_on && tgrp == 0;                           // these threads hold the row from here on
         if (lead) {
-            for (int k = 1; k < GROUPS; ++k) {
+            for (int k = 1; k < gt; ++k) {
                 const float4 v = sm_red[k * ITEMS + item];
                 o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
             }

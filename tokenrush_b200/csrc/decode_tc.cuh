@@ -6,8 +6,9 @@
 // codes of the cache straight from the TMA tile.  The products are laid out transposed, so
 // that the 128-row operand is always the cache tile and the few query rows are the N extent:
 //     S^T[128 keys x 2N]  = K . [Qhi ; Qlo]^T      A = K tile (K-major),  B = stacked query block
-//     O^T[128 dims x 2N] += V^T . [Phi ; Plo]^T    A = V tile (MN-major), B = stacked probabilities
-// (two O^T accumulators for the 256 dims).  hi + lo are two e4m3 terms of a value (8 significant
+//     O^T[128 dims x 2N] += V^T . [Phi ; Plo]^T    A = V tile (MN-major), B = probabilities, keys x rows
+// (two O^T accumulators for the 256 dims).  The probability tile is stored [key][row] (MN-major
+// B operand): a thread owns one key, so its 16 rows are one 16-byte store.  hi + lo are two e4m3 terms of a value (8 significant
 // bits, what bf16 carries); stacking them as 2N operand rows reads each cache tile once per
 // product, and the two partial results are added after the tensor-memory load.
 //
@@ -16,8 +17,10 @@
 // producer warp and one MMA issuer warp: 192, 320 or 448 threads for up to 16, 32, 48 rows.  The
 // warpgroups work independently on their rows (own named barrier, own statistics), so the work
 // per thread does not grow with M.  S^T and P are double-buffered.  Row maxima over the keys of
-// a tile are warp reductions (redux.sync.max.f32) followed by a 4-warp exchange through shared
-// memory; an O^T column is rescaled only when its row maximum moved.  The CTA's result goes to the split workspace in the layout of decode_kernel, and the
+// a row follow lazily: the stored probability is 2^(t - ref + 7), and ref moves only when a score
+// exceeds it by more than 1.75 (one barrier with an OR reduction per tile detects that); only
+// then the exact tile maxima are found (redux.sync.max.f32 + a 4-warp exchange) and the row's O^T
+// column and sum are rescaled.  The CTA's result goes to the split workspace in the layout of decode_kernel, and the
 // same ticket + tail finishes the launch.  Every wait is bounded.
 #pragma once
 #include "tc.cuh"
@@ -34,11 +37,11 @@ constexpr int TC_OFF_K = 0;
 constexpr int TC_OFF_V = TC_OFF_K + TC_KSLOTS * TC_TILE;
 constexpr int TC_OFF_Q = TC_OFF_V + TC_VSLOTS * TC_TILE;          // [2 column blocks][2N rows][128 B]
 constexpr int TC_Q_BYTES = 2 * TC_MAX_N2 * 128;
-constexpr int TC_OFF_P = TC_OFF_Q + TC_Q_BYTES;                    // 2 buffers of [2N rows][128 B]
-constexpr int TC_P_BYTES = TC_MAX_N2 * 128;
+constexpr int TC_OFF_P = TC_OFF_Q + TC_Q_BYTES;                    // 2 buffers of [128 keys][128 B: hi rows | lo rows | zeros]
+constexpr int TC_P_BYTES = TC_BN * 128;
 constexpr int TC_OFF_SC = TC_OFF_P + 2 * TC_P_BYTES;               // [KSLOTS][2][128] floats
 constexpr int TC_OFF_ST = TC_OFF_SC + TC_KSLOTS * 2 * TC_BN * 4;   // per-row statistics, see below
-constexpr int TC_ST_FLOATS = 4 * 48 + 4 * 48 + 8;
+constexpr int TC_ST_FLOATS = 2 * 4 * 48 + 2 * 48 + 8;
 constexpr int TC_OFF_BAR = TC_OFF_ST + TC_ST_FLOATS * 4;
 constexpr int TC_SMEM = TC_OFF_BAR + 256 + 1024;
 constexpr int TC_TMEM_COLS = 512;
@@ -49,6 +52,16 @@ __device__ __forceinline__ float redux_max(float v) {
     float r;
     asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
     return r;
+}
+constexpr float TC_LAG = 1.75f;                // a score may exceed its row's reference exponent by this much
+// bar.red: barrier over `threads` threads of barrier `id`, returning the OR of their predicates
+__device__ __forceinline__ bool barrier_or(int id, int threads, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+        "bar.red.or.pred q, %2, %3, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r) : "r"((uint32_t)pred), "r"(id), "r"(threads) : "memory");
+    return r != 0;
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     uint32_t r[16];
@@ -67,6 +80,13 @@ __device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, float (&v)[16])
         : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]), "=f"(v[9]),
           "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
         : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(v[8]), "f"(v[9]),
+          "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15])
+        : "memory");
 }
 __device__ __forceinline__ float tmem_ld1(uint32_t taddr) {
     uint32_t r;
@@ -87,13 +107,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     extern __shared__ uint8_t tc_smem_raw[];
     uint8_t *smem = tc_smem_raw + ((1024u - (smem_u32(tc_smem_raw) & 1023u)) & 1023u);
     float *sm_sc = reinterpret_cast<float *>(smem + TC_OFF_SC);
-    float *sm_wmax = reinterpret_cast<float *>(smem + TC_OFF_ST);        // [4][48] warp maxima / warp sums
-    float *sm_mnew = sm_wmax + 4 * 48;                                    // [48] running row maxima
-    float *sm_alpha = sm_mnew + 48;                                       // [48] factor of the rows whose maximum moved
-    float *sm_qinv = sm_alpha + 48;                                       // [48] inverse of the query row scale
+    float *sm_wmax = reinterpret_cast<float *>(smem + TC_OFF_ST);        // [2 buffers][row group][4 quarters][16] warp maxima / sums
+    float *sm_qinv = sm_wmax + 2 * 4 * 48;                                // [48] inverse of the query row scale
     int *sm_hi = reinterpret_cast<int *>(sm_qinv + 48);                   // [48] last visible key of a row
-    uint32_t *sm_moved = reinterpret_cast<uint32_t *>(sm_hi + 48);        // [2] bit masks of moved rows
-    int *sm_flag = reinterpret_cast<int *>(sm_moved + 2);                 // [3] used by decode_tail
+    int *sm_flag = sm_hi + 48;                                            // [3] used by decode_tail
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sm_flag + 3);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + TC_OFF_BAR);
     uint64_t *k_full = bars, *k_free = bars + 3, *v_full = bars + 6, *v_free = bars + 8;
@@ -177,32 +194,35 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const unsigned int epoch = tid == 0 ? *(volatile unsigned int *)&p.counters[128 + j] : 0u;
 
     // ---- query block: rows r of this kv head (query r / g, head j g + r % g) as two stacked e4m3
-    // copies with a power-of-two row scale; thread = (row, 64-dim quarter)
+    // copies with a power-of-two row scale; thread = (row, 32-dim eighth).  (The bytes of a
+    // probability row beyond its 2N codes are never written: they only feed O^T columns that
+    // nobody reads.)
     {
-        const int row = tid >> 2, quarter = tid & 3;
+        const int row = tid >> 3, part = tid & 7;
         const bool in_block = row < NROW, valid = row < p.rows && in_block;
         const int qi = valid ? row / p.g : 0, hq = valid ? j * p.g + row % p.g : 0;
-        const __nv_bfloat16 *qp = p.q + ((long long)qi * p.hq + hq) * D + quarter * 64;
-        uint4 raw[8];
+        const __nv_bfloat16 *qp = p.q + ((long long)qi * p.hq + hq) * D + part * 32;
+        uint4 raw[4];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) raw[c] = valid ? __ldg(reinterpret_cast<const uint4 *>(qp) + c) : make_uint4(0u, 0u, 0u, 0u);
+        for (int c = 0; c < 4; ++c) raw[c] = valid ? __ldg(reinterpret_cast<const uint4 *>(qp) + c) : make_uint4(0u, 0u, 0u, 0u);
         float amax = 0.f;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
             const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[c]);
 #pragma unroll
             for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(b2[e]); amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y))); }
         }
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
         amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
         int e = (int)((__float_as_uint(amax) >> 23) & 0xffu) - 127;
         if (amax == 0.f || e < -90 || !valid) e = 7;
         if (e > 90) e = 90;
         const float sc = valid ? __uint_as_float((uint32_t)(127 + 7 - e) << 23) : 0.f;
         if (in_block) {
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {                                  // 16 dims per chunk
-                const int c = quarter * 4 + cc;
+            for (int cc = 0; cc < 2; ++cc) {                                  // 16 dims per chunk
+                const int c = part * 2 + cc;
                 uint32_t hw[4], lw[4];
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
@@ -216,12 +236,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 *reinterpret_cast<uint4 *>(smem + TC_OFF_Q + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
                 *reinterpret_cast<uint4 *>(smem + TC_OFF_Q + off + NROW * 128) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
             }
-            if (quarter == 0) {
+            if (part == 0) {
                 sm_qinv[row] = __uint_as_float((uint32_t)(127 - 7 + e) << 23);
                 int hi = lloc_i - 1;
                 if (p.new_rows && pos_loc + qi < hi) hi = pos_loc + qi;
                 sm_hi[row] = hi;
-                sm_mnew[row] = -INFINITY;
             }
         }
     }
@@ -241,7 +260,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         // ================================ MMA issuer ==================================
         // order on the tensor pipe: QK(0), QK(1), PV(0), QK(2), PV(1), ...
         const uint32_t q_sm = smem_u32(smem + TC_OFF_Q), p_sm = smem_u32(smem + TC_OFF_P);
-        constexpr uint32_t IDESC_QK = umma_idesc_f8(TC_BN, N2, false, false), IDESC_PV = umma_idesc_f8(128, N2, true, false);
+        constexpr uint32_t IDESC_QK = umma_idesc_f8(TC_BN, N2, false, false), IDESC_PV = umma_idesc_f8(128, 128, true, true);
         auto issue_qk = [&](int i) -> bool {
             const int s = i % TC_KSLOTS, b = i & 1;
             if (!mbar_wait(&k_full[s], (i / TC_KSLOTS) & 1)) return false;
@@ -277,7 +296,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const uint64_t a = umma_desc(vt + h * (TC_BN * 128) + k * (32 * 128), TC_BN * 128, 1024);
-                        const uint64_t bd = umma_desc(pb + k * 32, 16, 1024);
+                        const uint64_t bd = umma_desc(pb + k * (32 * 128), TC_BN * 128, 1024);
                         tc_mma_f8(tmem + TC_TMEM_O + h * 128, a, bd, IDESC_PV, (i | k) ? 1u : 0u);
                     }
                 tc_commit(&v_free[b]);
@@ -291,17 +310,23 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         const int kl = qw * 32 + lane;                                         // 0..127
         const int r0 = rg * 16;                                                // first row of this group
         const uint32_t lane_addr = tmem + ((uint32_t)(qw * 32) << 16);
-        const uint32_t p_chunk = (uint32_t)(kl >> 4), p_byte = (uint32_t)(kl & 15);
         const int all_hi = p.new_rows ? (pos_loc < lloc_i - 1 ? pos_loc : lloc_i - 1) : lloc_i - 1;
-        float *g_wmax = sm_wmax + rg * 64;                                     // [4 quarters][16 rows]
-        float *g_mnew = sm_mnew + r0, *g_alpha = sm_alpha + r0;
         const float *g_qinv = sm_qinv + r0;
         const int *g_hi = sm_hi + r0;
         const int bar_id = 1 + rg;
-        float lsum[16];
+        // this thread's two 16-byte slots in a probability row: hi codes of rows r0.., lo codes of rows r0..
+        const uint32_t p_hi_off = (uint32_t)kl * 128u + ((((uint32_t)rg) ^ ((uint32_t)kl & 7u)) << 4);
+        const uint32_t p_lo_off = (uint32_t)kl * 128u + ((((uint32_t)(NCH + rg)) ^ ((uint32_t)kl & 7u)) << 4);
+        // Reference exponent of a row: probabilities are stored as 2^(t - ref + 7).  ref follows the
+        // row maximum lazily: it moves (and the row's O^T column and sum are rescaled) only when a
+        // score exceeds it by more than TC_LAG, so that the stored value stays below the e4m3
+        // maximum (2^(7 + 1.75) = 430 < 448).  cref = 7 - ref, identical in every thread of the group;
+        // a row is `unset` until its first visible key.
+        float lsum[16], cref[16];
 #pragma unroll
-        for (int r = 0; r < 16; ++r) lsum[r] = 0.f;
-        float m_own = -INFINITY;                                               // threads kl < 16: running maximum of row r0 + kl
+        for (int r = 0; r < 16; ++r) { lsum[r] = 0.f; cref[r] = 0.f; }
+        uint32_t unset = 0xffffu;
+        float *g_wmax = sm_wmax + rg * 64;                                     // [4 quarters][16 rows], slow path only
 
         for (int i = 0; i < my_tiles && ok; ++i) {
             const int s = i % TC_KSLOTS, b = i & 1;
@@ -313,7 +338,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             const bool key_ok = kv < lloc_i && vsc > 0.f;
             const float kfac = ksc * p.scale_log2;
             const float vlog = key_ok ? __log2f(vsc) : 0.f;
-            const float vinv = key_ok ? __fdividef(0.00390625f, vsc) : 0.f;     // 1 / (256 v_scale)
+            const float vinv = key_ok ? __fdividef(0.0078125f, vsc) : 0.f;      // 1 / (128 v_scale)
             if (!(ok = mbar_wait(&s_full[b], (i >> 1) & 1))) break;
             tc_fence_after();
             float tv[16];
@@ -325,10 +350,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     const float4 qv = *reinterpret_cast<const float4 *>(&g_qinv[q4 * 4]);
-                    tv[q4 * 4 + 0] = fmaf((hi[q4 * 4 + 0] + lo[q4 * 4 + 0]) * kfac, qv.x, vlog);
-                    tv[q4 * 4 + 1] = fmaf((hi[q4 * 4 + 1] + lo[q4 * 4 + 1]) * kfac, qv.y, vlog);
-                    tv[q4 * 4 + 2] = fmaf((hi[q4 * 4 + 2] + lo[q4 * 4 + 2]) * kfac, qv.z, vlog);
-                    tv[q4 * 4 + 3] = fmaf((hi[q4 * 4 + 3] + lo[q4 * 4 + 3]) * kfac, qv.w, vlog);
+                    tv[q4 * 4 + 0] = fmaf((hi[q4 * 4 + 0] + lo[q4 * 4 + 0]) * kfac, qv.x, vlog + cref[q4 * 4 + 0]);
+                    tv[q4 * 4 + 1] = fmaf((hi[q4 * 4 + 1] + lo[q4 * 4 + 1]) * kfac, qv.y, vlog + cref[q4 * 4 + 1]);
+                    tv[q4 * 4 + 2] = fmaf((hi[q4 * 4 + 2] + lo[q4 * 4 + 2]) * kfac, qv.z, vlog + cref[q4 * 4 + 2]);
+                    tv[q4 * 4 + 3] = fmaf((hi[q4 * 4 + 3] + lo[q4 * 4 + 3]) * kfac, qv.w, vlog + cref[q4 * 4 + 3]);
                 }
             }
             tc_fence_before();
@@ -339,81 +364,87 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 for (int r = 0; r < 16; ++r)
                     if (!(key_ok && kv <= g_hi[r])) tv[r] = -INFINITY;
             }
-            // ---- row maxima over the 128 keys: warp reduction, then the four warps through shared memory
-            {
-                float wm[16];
+            // ---- does any score of the group exceed its row's reference by more than the lag (or reach a
+            // row that has none yet)?  One barrier with an OR reduction answers for the four warps.
+            float tmax = tv[0];
 #pragma unroll
-                for (int r = 0; r < 16; ++r) wm[r] = redux_max(tv[r]);
-                if (lane == 0) {
+            for (int r = 1; r < 16; ++r) tmax = fmaxf(tmax, tv[r]);
+            bool danger = tmax > 7.f + TC_LAG;
+            if (unset) {
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4)
-                        *reinterpret_cast<float4 *>(&g_wmax[qw * 16 + q4 * 4]) = make_float4(wm[q4 * 4], wm[q4 * 4 + 1], wm[q4 * 4 + 2], wm[q4 * 4 + 3]);
+                for (int r = 0; r < 16; ++r) danger |= ((unset >> r) & 1u) && tv[r] > -INFINITY;
+            }
+            if (barrier_or(bar_id, 128, danger)) {
+                // slow path: exact row maxima of this tile (warp reduction, the four quarters through
+                // shared memory); rows beyond the lag get the tile maximum as their new reference
+                {
+                    float wm[16];
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) wm[r] = redux_max(tv[r]);
+                    if (lane == 0) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4)
+                            *reinterpret_cast<float4 *>(&g_wmax[qw * 16 + q4 * 4]) = make_float4(wm[q4 * 4], wm[q4 * 4 + 1], wm[q4 * 4 + 2], wm[q4 * 4 + 3]);
+                    }
+                }
+                named_barrier(bar_id, 128);
+                float al[16];
+                uint32_t upd = 0u;
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const float gm = fmaxf(fmaxf(g_wmax[r], g_wmax[16 + r]), fmaxf(g_wmax[32 + r], g_wmax[48 + r]));
+                    const bool u = gm > 7.f + TC_LAG || (((unset >> r) & 1u) && gm > -INFINITY);
+                    const float delta = u ? gm - 7.f : 0.f;                    // new reference = the tile maximum
+                    al[r] = ((unset >> r) & 1u) ? 0.f : fast_exp2(-delta);     // a row without reference has no sum and a zero column yet
+                    cref[r] -= delta;
+                    tv[r] -= delta;
+                    lsum[r] *= al[r];
+                    upd |= (u ? 1u : 0u) << r;
+                }
+                unset &= ~upd;
+                if (i > 0) {
+                    // correct the O^T columns of the updated rows; PV(i-1) must have landed
+                    if (!(ok = mbar_wait(&pv_done[b ^ 1], ((i - 1) >> 1) & 1))) break;
+                    tc_fence_after();
+#pragma unroll 1
+                    for (uint32_t mk = upd; mk; mk &= mk - 1) {
+                        const int rr = __ffs(mk) - 1;
+                        const float a_r = al[rr];
+                        const uint32_t a0 = lane_addr + TC_TMEM_O + r0 + rr, a1 = a0 + NROW, a2 = a0 + 128, a3 = a2 + NROW;
+                        float o0 = tmem_ld1(a0), o1 = tmem_ld1(a1), o2 = tmem_ld1(a2), o3 = tmem_ld1(a3);
+                        tmem_wait_ld();
+                        tmem_st1(a0, o0 * a_r); tmem_st1(a1, o1 * a_r); tmem_st1(a2, o2 * a_r); tmem_st1(a3, o3 * a_r);
+                    }
+                    tmem_wait_st();
                 }
             }
-            named_barrier(bar_id, 128);
-            if (qw == 0) {                                                     // one thread per row
-                bool moved = false;
-                if (lane < 16) {
-                    const float mt = fmaxf(fmaxf(g_wmax[lane], g_wmax[16 + lane]), fmaxf(g_wmax[32 + lane], g_wmax[48 + lane]));
-                    const float mn = fmaxf(m_own, mt);
-                    moved = mn != m_own && i > 0;
-                    g_alpha[lane] = mn == -INFINITY ? 1.f : fast_exp2(m_own - mn);
-                    g_mnew[lane] = mn;
-                    m_own = mn;
-                }
-                const uint32_t mask = __ballot_sync(0xffffffffu, moved);
-                if (lane == 0) sm_moved[rg] = mask;
-            }
-            named_barrier(bar_id, 128);
-            uint32_t mk = sm_moved[rg];
-            // the P buffer of tile i-2 must have been consumed; a correction needs PV(i-1) complete
+            // the P buffer of tile i-2 must have been consumed
             if (i >= 2 && !(ok = mbar_wait(&pv_done[b], ((i >> 1) & 1) ^ 1))) break;
-            if (mk) {
-                if (!(ok = mbar_wait(&pv_done[b ^ 1], ((i - 1) >> 1) & 1))) break;
-                tc_fence_after();
-                while (mk) {
-                    const int rr = __ffs(mk) - 1;
-                    mk &= mk - 1;
-                    const float al = g_alpha[rr];
-                    const uint32_t a0 = lane_addr + TC_TMEM_O + r0 + rr, a1 = a0 + NROW, a2 = a0 + 128, a3 = a2 + NROW;
-                    float o0 = tmem_ld1(a0), o1 = tmem_ld1(a1), o2 = tmem_ld1(a2), o3 = tmem_ld1(a3);
-                    tmem_wait_ld();
-                    tmem_st1(a0, o0 * al); tmem_st1(a1, o1 * al); tmem_st1(a2, o2 * al); tmem_st1(a3, o3 * al);
-                }
-                tmem_wait_st();
+            // ---- probabilities 2^(t - ref + 7) as hi + lo e4m3 codes: this key's 16 rows are 16 + 16 bytes
+            uint32_t hw[4], lw[4];
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const float4 al = *reinterpret_cast<const float4 *>(&g_alpha[q4 * 4]);
-                    lsum[q4 * 4 + 0] *= al.x; lsum[q4 * 4 + 1] *= al.y; lsum[q4 * 4 + 2] *= al.z; lsum[q4 * 4 + 3] *= al.w;
-                }
-            }
-            // ---- probabilities (x 256) as hi + lo e4m3 codes, one byte per (row, key): rows of 128 keys
-            uint8_t *pb = smem + TC_OFF_P + b * TC_P_BYTES + r0 * 128;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                const float4 mn = *reinterpret_cast<const float4 *>(&g_mnew[q4 * 4]);
-                const float ms[4] = {mn.x == -INFINITY ? 0.f : mn.x, mn.y == -INFINITY ? 0.f : mn.y,
-                                     mn.z == -INFINITY ? 0.f : mn.z, mn.w == -INFINITY ? 0.f : mn.w};
+            for (int w = 0; w < 4; ++w) {
+                uint32_t hc[2], lc[2];
 #pragma unroll
                 for (int h2 = 0; h2 < 2; ++h2) {
-                    const int r = q4 * 4 + 2 * h2;
-                    const float p0 = fast_exp2(tv[r] - ms[2 * h2] + 8.f), p1 = fast_exp2(tv[r + 1] - ms[2 * h2 + 1] + 8.f);
-                    uint32_t hc, lc;
-                    const float2 pq = pf_split2_hq(p0, p1, hc, lc);            // the weights as the MMA sees them
+                    const int r = w * 4 + 2 * h2;
+                    const float p0 = fast_exp2(tv[r]), p1 = fast_exp2(tv[r + 1]);
+                    const float2 pq = pf_split2_hq(p0, p1, hc[h2], lc[h2]);    // the weights as the MMA sees them
                     lsum[r] = fmaf(pq.x, vinv, lsum[r]);
                     lsum[r + 1] = fmaf(pq.y, vinv, lsum[r + 1]);
-                    uint8_t *d0 = pb + r * 128 + (((p_chunk ^ (uint32_t)(r & 7)) << 4) | p_byte);
-                    uint8_t *d1 = pb + (r + 1) * 128 + (((p_chunk ^ (uint32_t)((r + 1) & 7)) << 4) | p_byte);
-                    d0[0] = (uint8_t)(hc & 0xffu); d1[0] = (uint8_t)(hc >> 8);
-                    d0[NROW * 128] = (uint8_t)(lc & 0xffu); d1[NROW * 128] = (uint8_t)(lc >> 8);
                 }
+                hw[w] = hc[0] | (hc[1] << 16);
+                lw[w] = lc[0] | (lc[1] << 16);
             }
+            uint8_t *pb = smem + TC_OFF_P + b * TC_P_BYTES;
+            *reinterpret_cast<uint4 *>(pb + p_hi_off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            *reinterpret_cast<uint4 *>(pb + p_lo_off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
             fence_async_smem();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_full[b]);
         }
-        // ---- epilogue: this CTA's partial rows.  acc[row][dim] = (hi + lo part of O^T[dim][row]) / 256
+        // ---- epilogue: this CTA's partial rows.  acc[row][dim] = (hi + lo part of O^T[dim][row]) / 128
         if (ok && my_tiles > 0) ok = mbar_wait(&pv_done[(my_tiles - 1) & 1], ((my_tiles - 1) >> 1) & 1);
         tc_fence_after();
         const long long part_base = ((long long)j * p.nsplit + split) * p.rows_pad;
@@ -431,31 +462,54 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
                 const int r = r0 + e;
-                if (r < p.rows) p.part_acc[(part_base + r) * D + h * 128 + kl] = (hi[e] + lo[e]) * 0.00390625f;
+                if (r < p.rows) p.part_acc[(part_base + r) * D + h * 128 + kl] = (hi[e] + lo[e]) * 0.0078125f;
             }
         }
         tc_fence_before();
-        // row sums over the 128 key lanes
+        // row sums over the 128 key lanes: a butterfly that halves the rows a lane carries per step
+        // (lane L ends with row L & 15 summed over the lanes of its half-warp), then one more step
+        float v8[8], v4[4], v2[2], v1;
+        {
+            const bool up = lane & 16;
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            float v = lsum[r];
-            v += __shfl_xor_sync(0xffffffffu, v, 16);
-            v += __shfl_xor_sync(0xffffffffu, v, 8);
-            v += __shfl_xor_sync(0xffffffffu, v, 4);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            lsum[r] = v;
+            for (int r = 0; r < 8; ++r) {
+                const float send = up ? lsum[r] : lsum[8 + r], keep = up ? lsum[8 + r] : lsum[r];
+                v8[r] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+            }
         }
-        if (lane == 0) {
+        {
+            const bool up = lane & 8;
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4)
-                *reinterpret_cast<float4 *>(&g_wmax[qw * 16 + q4 * 4]) = make_float4(lsum[q4 * 4], lsum[q4 * 4 + 1], lsum[q4 * 4 + 2], lsum[q4 * 4 + 3]);
+            for (int r = 0; r < 4; ++r) {
+                const float send = up ? v8[r] : v8[4 + r], keep = up ? v8[4 + r] : v8[r];
+                v4[r] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+            }
         }
+        {
+            const bool up = lane & 4;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const float send = up ? v4[r] : v4[2 + r], keep = up ? v4[2 + r] : v4[r];
+                v2[r] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+            }
+        }
+        {
+            const bool up = lane & 2;
+            const float send = up ? v2[0] : v2[1], keep = up ? v2[1] : v2[0];
+            v1 = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+        }
+        v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+        // lane L now holds the warp's sum of row 8 b4 + 4 b3 + 2 b2 + b1 (b = bits of L), twice (b0)
+        const int my_row = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+        float *g_sum = sm_wmax + 4 * 48 + rg * 64;                              // not the slow path's buffer
+        if (!(lane & 1)) g_sum[qw * 16 + my_row] = v1;
         named_barrier(bar_id, 128);
         if (kl < 16 && r0 + kl < p.rows) {
-            const float l = (g_wmax[kl] + g_wmax[16 + kl]) + (g_wmax[32 + kl] + g_wmax[48 + kl]);
-            p.part_ml[(part_base + r0 + kl) * 2 + 0] = m_own;
-            p.part_ml[(part_base + r0 + kl) * 2 + 1] = l;
+            const float l = (g_sum[kl] + g_sum[16 + kl]) + (g_sum[32 + kl] + g_sum[48 + kl]);
+            float cr = 0.f;                                                    // cref[kl] without dynamic register indexing
+#pragma unroll
+            for (int r = 0; r < 16; ++r) cr = kl == r ? cref[r] : cr;
+            *reinterpret_cast<float2 *>(&p.part_ml[(part_base + r0 + kl) * 2]) = make_float2(((unset >> kl) & 1u) ? -INFINITY : 7.f - cr, l);
         }
     }
     __syncthreads();
