@@ -22,11 +22,11 @@
 //     shards) the GPUs are all merged with the same log-sum-exp formula in a fixed order;
 //   * every CTA writes one (max, sum, acc) partial per row and takes an atomic ticket of its
 //     kv head; the last arrival resets the counters (so the launch replays inside a CUDA
-//     graph) and publishes an epoch.  The last `rows` arrivals stay (bounded wait on the
-//     epoch) and claim output rows one at a time: a row's split partials are fetched in one
-//     round trip, merged in split order, gated if asked, and written as bf16 - or, for a
-//     sequence shard, pushed to the peers' exchange buffers and merged in rank order.  The
-//     last arrival claims until no row is left, so completeness never needs co-residency.
+//     graph) and publishes an epoch.  The last arrivals, as many as there are output rows
+//     (or row pairs), stay (bounded wait on the epoch) and take the rows that their arrival
+//     number assigns them: a row's split partials are fetched in one round trip, merged in
+//     split order, gated if asked, and written as bf16 - or, for a sequence shard, pushed to
+//     the peers' exchange buffers and merged in rank order.
 //   * programmatic dependent launch: tiles that the preceding append cannot touch are
 //     requested before griddepcontrol.wait, so the prologue overlaps the append's tail.
 //
@@ -114,37 +114,40 @@ template <int D, int NTHREADS>
 __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem, int *sm_flag, const int j, const int active,
                                             const unsigned int epoch) {
     const int tid = threadIdx.x, lane = threadIdx.x & 31;
-    // 2. ticket.  The last CTA of this kv head to arrive publishes a new epoch; CTAs that arrived
-    // earlier wait for it (bounded) and then every CTA present claims output rows one at a time
-    // and merges them, so the combine runs on many SMs.  The last CTA keeps claiming until no
-    // row is left, so the result is complete even if every helper gave up waiting.
-    unsigned int *ticket = p.counters + j, *claim = p.counters + 64 + j, *seq = p.counters + 128 + j;
+    // 2. ticket.  The rows are merged by the last CTAs of this kv head to arrive, one claim (one or
+    // two rows) each: arrival number `old` makes a CTA helper number old - (active - helpers), and a
+    // helper takes the claims h, h + helpers, ...  Earlier arrivals leave at once and free their SM
+    // for the next kernel in the stream.  The last arrival resets the ticket (the launch replays
+    // inside a graph) and publishes a new epoch; the other helpers wait for it (bounded: a helper
+    // that gives up records TRB_ST_WAIT_TIMEOUT, its rows are then missing).
+    unsigned int *ticket = p.counters + j, *seq = p.counters + 128 + j;
     constexpr int ITEMS = D / 4, GROUPS = NTHREADS / ITEMS;
     const int rc = (p.rows > active && p.p2p_world == 0 && GROUPS >= 2) ? 2 : 1;     // rows per claim, see below
+    const int nclaims = (p.rows + rc - 1) / rc;
+    const int helpers = nclaims < active ? nclaims : active;
     __threadfence();
     __syncthreads();
     if (tid == 0) {
         const unsigned int old = atomicAdd(ticket, 1u);
-        int state = old == (unsigned int)(active - 1) ? 2 : 1;
-        if (state == 2) {
+        int h = (int)old - (active - helpers);
+        if (old == (unsigned int)(active - 1)) {
             *ticket = 0u;                                               // ready for the next launch / replay
-            *claim = 0u;
             __threadfence();
             *(volatile unsigned int *)seq = epoch + 1u;
-        } else {
-            state = 0;
-            // only the last arrivals (one per claim; a claim is one or two rows) can find a row to merge;
-            // earlier ones leave at once and free their SM for the next kernel in the stream
-            for (int it = 0; it < 4096 && (int)old >= active - (p.rows + rc - 1) / rc; ++it) {
-                if (*(volatile unsigned int *)seq == epoch + 1u) { state = 1; break; }
-                __nanosleep(100);
+        } else if (h >= 0) {
+            bool seen = false;
+            for (int it = 0; it < (1 << 17); ++it) {
+                if (*(volatile unsigned int *)seq == epoch + 1u) { seen = true; break; }
+                __nanosleep(it < 64 ? 20 : 200);
             }
+            if (!seen) { raise_status(TRB_ST_WAIT_TIMEOUT); h = -1; }
         }
-        *sm_flag = state;
+        *sm_flag = h;
         sm_flag[2] = (int)epoch;
     }
     __syncthreads();
-    if (*sm_flag == 0) return;                                          // gave up waiting: the others finish the rows
+    const int helper = *sm_flag;
+    if (helper < 0) return;
     __threadfence();
 
     // 3. tail: LSE merge of the output rows over the active splits (+ extra partials), in split
@@ -162,13 +165,9 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
     float *sm_l = sm_m + (DEC_MAX_SPLITS + 4);                          // [n_parts]
     float4 *sm_red = reinterpret_cast<float4 *>(reinterpret_cast<float *>(smem) + 4 * (DEC_MAX_SPLITS + 4)) +
                      (in_team ? team : 0) * gt * ITEMS;                 // [gt][ITEMS] per team
-    int *sm_claim = sm_flag + 1;
-    for (;;) {
-        __syncthreads();
-        if (tid == 0) *sm_claim = (int)atomicAdd(claim, 1u);
-        __syncthreads();
-        if (*sm_claim * rc >= p.rows) break;
-        const int row = *sm_claim * rc + team;
+    for (int c = helper; c < nclaims; c += helpers) {
+        if (c != helper) __syncthreads();                               // the scratch of the previous claim is free
+        const int row = c * rc + team;
         const bool row_on = in_team && row < p.rows;
         const int qi = row_on ? row / p.g : 0, hq = row_on ? j * p.g + row % p.g : 0;
         const long long grow = (long long)qi * p.hq + hq;
