@@ -50,9 +50,10 @@ WORKLOADS = {
     "verify64k": dict(ctx=65536, m=8),
     "prefill8k": dict(ctx=131072, t=8192),
 }
-# DRAM bytes per live row per layer-launch of the decode kernel from the ncu capture summarised in
-# profiles/decode_kernel_fp8_m1_window256k.md (dram__bytes_read.sum + dram__bytes_write.sum over 131072 rows)
-NCU_TRAFFIC_BYTES_PER_ROW = 2114
+# DRAM bytes per live row per layer-launch of the decode kernels (dram__bytes_read.sum +
+# dram__bytes_write.sum of one ncu capture, divided by the rows of that launch), by query rows M:
+# profiles/decode_kernel_fp8_m1_window256k.md (131072 rows) and profiles/decode_tc_kernel_m8_verify64k.md (65536 rows)
+NCU_TRAFFIC_BYTES_PER_ROW = {1: 2114, 8: 2164}
 
 
 def measured_peaks():
@@ -262,10 +263,10 @@ def run_product(args):
         us_launch = ms_k * 1e3 / (reps * LAYERS)
         achieved = live_now * ROW_BYTES / (us_launch * 1e-6) / 1e9
         peaks, how = measured_peaks()
-        roofline = {"bound": "hbm", "kernel": "decode_kernel<256, fp8>", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+        roofline = {"bound": "hbm", "kernel": "decode_kernel<256, fp8>" if m == 1 else "decode_tc_kernel (tcgen05)", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                     "peak_source": how, "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                     "us_per_launch": round(us_launch, 2), "algorithmic_bytes_per_launch": live_now * ROW_BYTES,
-                    "traffic": (NCU_TRAFFIC_BYTES_PER_ROW * live_now) if NCU_TRAFFIC_BYTES_PER_ROW else None}
+                    "traffic": (NCU_TRAFFIC_BYTES_PER_ROW[m] * live_now) if m in NCU_TRAFFIC_BYTES_PER_ROW else None}
         cpu_baseline = run_cpu_sample(ctx, m, budget_s=args.cpu_seconds)
 
     status = tb._lib.device_status()
@@ -274,7 +275,7 @@ def run_product(args):
             "metric": "decode_attn_effective_kv_bandwidth", "value": round(value, 1), "unit": "GB/s",
             "us_per_step": round(ms * 1e3 / steps, 2), "ms_per_step": round(ms / steps, 5),
             "n_gpus": world, "steps": steps, "warmup": warmup, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 cache, f16 MMA, fp32 softmax/accumulate",
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 cache, f16 MMA, fp32 softmax/accumulate" if m == 1 else "fp8_e4m3 cache and operands (q, p as hi+lo pairs), fp32 accumulate in TMEM",
             "data": "synthetic",
             "config": {"workload": args.workload, "layers": LAYERS, "context_rows": ctx, "query_rows": m,
                        "heads": f"{HQ}q/{HKV}kv x {D}", "kv_bytes_per_step": LAYERS * ROW_BYTES * live_first,
