@@ -125,9 +125,12 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
     const int rc = (p.rows > active && p.p2p_world == 0 && GROUPS >= 2) ? 2 : 1;     // rows per claim, see below
     const int nclaims = (p.rows + rc - 1) / rc;
     const int helpers = nclaims < active ? nclaims : active;
-    __threadfence();
+    // release / acquire through one thread: the barrier orders the CTA's partial stores before
+    // thread 0's fence, the fence makes them visible before the ticket; on the way back the fence
+    // after the epoch was seen comes before the barrier that lets the other threads load
     __syncthreads();
     if (tid == 0) {
+        __threadfence();
         const unsigned int old = atomicAdd(ticket, 1u);
         int h = (int)old - (active - helpers);
         if (old == (unsigned int)(active - 1)) {
@@ -142,13 +145,13 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
             }
             if (!seen) { raise_status(TRB_ST_WAIT_TIMEOUT); h = -1; }
         }
+        __threadfence();
         *sm_flag = h;
         sm_flag[2] = (int)epoch;
     }
     __syncthreads();
     const int helper = *sm_flag;
     if (helper < 0) return;
-    __threadfence();
 
     // 3. tail: LSE merge of the output rows over the active splits (+ extra partials), in split
     // order: thread (item, group) sums the splits of its group, the groups are added in group
@@ -234,60 +237,67 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
             }
             continue;
         }
-        if (p.p2p_world > 0) {
+        if (p.p2p_world > 1 && lead) {
             // ---- sequence shards: exchange this row's (max, sum, acc) with the other GPUs by peer
-            // stores, wait (bounded) for theirs, merge in rank order.  The tag is this kv head's launch
-            // epoch, identical on all GPUs because they make the same calls on their workspaces.
-            // This GPU's own partial stays in registers; only the peers' go through memory.
+            // stores, wait (bounded) for theirs, merge in rank order.  Every 8 bytes that cross the
+            // link are (value, tag): the receiver polls the data itself, so there is no flag, no fence
+            // and no second message.  The tag is this kv head's launch epoch + 1, identical on all GPUs
+            // because they make the same calls on their workspaces; slots rotate over P2P_SLOTS calls
+            // (a GPU cannot be more than one call ahead of a peer whose packets it waits for).  This
+            // GPU's own partial stays in registers.
             const P2PLayout xl = p2p_layout(p.p2p_world, p.m * p.hq, D);
             const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
             const size_t slot = tag % P2P_SLOTS;
             const size_t nrow = (size_t)(p.m * p.hq);
-            if (lead) {
-                for (int r = 0; r < p.p2p_world; ++r) {
-                    if (r == p.p2p_rank) continue;
-                    float *dst = (float *)((uint8_t *)p.p2p_ptr[r] + xl.data) + ((slot * p.p2p_world + p.p2p_rank) * nrow + grow) * xl.row_floats;
-                    *reinterpret_cast<float4 *>(dst + d4) = o;
-                    if (item == 0) *reinterpret_cast<float2 *>(dst + D) = make_float2(mmax, lsum);
-                }
-                __threadfence_system();
+            const uint4 k0 = make_uint4(__float_as_uint(o.x), tag, __float_as_uint(o.y), tag);
+            const uint4 k1 = make_uint4(__float_as_uint(o.z), tag, __float_as_uint(o.w), tag);
+            const uint4 k2 = make_uint4(__float_as_uint(mmax), tag, __float_as_uint(lsum), tag);
+            for (int r = 0; r < p.p2p_world; ++r) {
+                if (r == p.p2p_rank) continue;
+                uint4 *dst = reinterpret_cast<uint4 *>((uint8_t *)p.p2p_ptr[r] + xl.ll) +
+                             (((slot * p.p2p_world + p.p2p_rank) * nrow + grow) * ITEMS + item) * 3;
+                st_volatile_v4(dst, k0); st_volatile_v4(dst + 1, k1); st_volatile_v4(dst + 2, k2);
             }
-            __syncthreads();
-            uint8_t *local = (uint8_t *)p.p2p_ptr[p.p2p_rank];
-            if (tid < p.p2p_world && tid != p.p2p_rank) {
-                volatile unsigned int *flag = (volatile unsigned int *)((uint8_t *)p.p2p_ptr[tid] + xl.flags) + (slot * p.p2p_world + p.p2p_rank) * nrow + grow;
-                *flag = tag;
-                const volatile unsigned int *mine = (const volatile unsigned int *)(local + xl.flags) + (slot * p.p2p_world + tid) * nrow + grow;
-                bool ok = false;
+            const uint4 *local = reinterpret_cast<const uint4 *>((const uint8_t *)p.p2p_ptr[p.p2p_rank] + xl.ll);
+            // pass 1: the peers' maxima (their third packet)
+            float gm = mmax;
+            bool ok = true;
+            for (int r = 0; r < p.p2p_world && ok; ++r) {
+                if (r == p.p2p_rank) continue;
+                const uint4 *src = local + (((slot * p.p2p_world + r) * nrow + grow) * ITEMS + item) * 3;
+                ok = false;
                 for (unsigned int it = 0; it < P2P_SPIN_LIMIT; ++it) {
-                    if (*mine == tag) { ok = true; break; }
+                    const uint4 v = ld_volatile_v4(src + 2);
+                    if (v.y == tag && v.w == tag) { gm = fmaxf(gm, __uint_as_float(v.x)); ok = true; break; }
                     if (it > 64) __nanosleep(100);
                 }
-                if (!ok) raise_status(TRB_ST_PEER_TIMEOUT);
-                __threadfence_system();
             }
-            __syncthreads();
-            if (lead && p.p2p_world > 1) {
-                const float *data = (const float *)(local + xl.data);
-                float gm = mmax;
-                for (int r = 0; r < p.p2p_world; ++r)
-                    if (r != p.p2p_rank) gm = fmaxf(gm, __ldcg(data + ((slot * p.p2p_world + r) * nrow + grow) * xl.row_floats + D));
-                float gl = 0.f;
-                float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int r = 0; r < p.p2p_world; ++r) {                  // rank order, own partial from registers
-                    float2 mlr = make_float2(mmax, lsum);
-                    float4 v = o;
-                    if (r != p.p2p_rank) {
-                        const float *src = data + ((slot * p.p2p_world + r) * nrow + grow) * xl.row_floats;
-                        mlr = __ldcg(reinterpret_cast<const float2 *>(src + D));
-                        v = __ldcg(reinterpret_cast<const float4 *>(src + d4));
+            // pass 2: weights and sums in rank order, own partial from registers
+            float gl = 0.f;
+            float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < p.p2p_world && ok; ++r) {
+                float2 mlr = make_float2(mmax, lsum);
+                float4 v = o;
+                if (r != p.p2p_rank) {
+                    const uint4 *src = local + (((slot * p.p2p_world + r) * nrow + grow) * ITEMS + item) * 3;
+                    ok = false;
+                    for (unsigned int it = 0; it < P2P_SPIN_LIMIT; ++it) {
+                        const uint4 a0 = ld_volatile_v4(src), a1 = ld_volatile_v4(src + 1), a2 = ld_volatile_v4(src + 2);
+                        if (a0.y == tag && a0.w == tag && a1.y == tag && a1.w == tag && a2.y == tag && a2.w == tag) {
+                            v = make_float4(__uint_as_float(a0.x), __uint_as_float(a0.z), __uint_as_float(a1.x), __uint_as_float(a1.z));
+                            mlr = make_float2(__uint_as_float(a2.x), __uint_as_float(a2.z));
+                            ok = true;
+                            break;
+                        }
+                        if (it > 64) __nanosleep(100);
                     }
-                    const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
-                    gl = fmaf(w, mlr.y, gl);
-                    go.x = fmaf(w, v.x, go.x); go.y = fmaf(w, v.y, go.y); go.z = fmaf(w, v.z, go.z); go.w = fmaf(w, v.w, go.w);
                 }
-                o = go; lsum = gl;
+                const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
+                gl = fmaf(w, mlr.y, gl);
+                go.x = fmaf(w, v.x, go.x); go.y = fmaf(w, v.y, go.y); go.z = fmaf(w, v.z, go.z); go.w = fmaf(w, v.w, go.w);
             }
+            if (!ok) raise_status(TRB_ST_PEER_TIMEOUT);
+            o = go; lsum = gl;
         }
         if (!lead) continue;
         const float inv = 1.f / lsum;

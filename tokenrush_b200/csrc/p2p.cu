@@ -4,8 +4,10 @@
 // were shared with cudaIpc handles at set-up, and merged on every GPU in rank order with
 // the same log-sum-exp formula that merges the splits of one GPU.
 //
-// One CTA per row: push the row to every peer, publish a per-row flag (release, system
-// scope), wait for every peer's flag of the same call with an iteration limit, merge.
+// Two forms.  Fused into the decode kernel's tail (the default): every 8 bytes sent are a
+// (value, tag) pair, the receiver polls the data itself.  As a separate kernel
+// (p2p_merge_kernel below), one CTA per row: push the row to every peer, publish a per-row flag
+// (release, system scope), wait for every peer's flag of the same call with an iteration limit, merge.
 // Flags carry the call's sequence number, so nothing is ever reset; buffers are used
 // round-robin over P2P_SLOTS calls, which is safe because a GPU can be at most one call
 // ahead of the slowest peer (it cannot pass its own wait).
@@ -18,7 +20,7 @@ constexpr int P2P_MAX_WORLD = 8;
 constexpr unsigned int P2P_SPIN_LIMIT = 1u << 22;     // about a second with the back-off below
 
 struct P2PLayout {
-    size_t flags, data, total;
+    size_t flags, data, ll, total;
     int row_floats;
 };
 __host__ __device__ inline P2PLayout p2p_layout(int world, int rows, int d) {
@@ -26,7 +28,10 @@ __host__ __device__ inline P2PLayout p2p_layout(int world, int rows, int d) {
     l.row_floats = d + 4;                                    // acc[d], max, sum, 2 pad floats (16-byte rows)
     l.flags = 256;                                           // header: ticket counter
     l.data = l.flags + (((size_t)P2P_SLOTS * world * rows * sizeof(unsigned int) + 255) / 256) * 256;
-    l.total = l.data + (size_t)P2P_SLOTS * world * rows * l.row_floats * sizeof(float);
+    // region of the exchange fused into the decode kernel's tail: per (slot, source rank, row) d / 4
+    // threads x 3 packets of 16 bytes, each 8 bytes a (value, tag) pair
+    l.ll = ((l.data + (size_t)P2P_SLOTS * world * rows * l.row_floats * sizeof(float) + 255) / 256) * 256;
+    l.total = l.ll + (size_t)P2P_SLOTS * world * rows * (d / 4) * 3 * 16;
     return l;
 }
 
@@ -40,6 +45,14 @@ struct P2PParams {
     long long gate_rs, gate_hs;
 };
 
+__device__ __forceinline__ void st_volatile_v4(uint4 *p, const uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
