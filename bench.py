@@ -53,7 +53,7 @@ WORKLOADS = {
 # DRAM bytes per live row per layer-launch of the decode kernels (dram__bytes_read.sum +
 # dram__bytes_write.sum of one ncu capture, divided by the rows of that launch), by query rows M:
 # profiles/decode_kernel_fp8_m1_window256k.md (131072 rows) and profiles/decode_tc_kernel_m8_verify64k.md (65536 rows)
-NCU_TRAFFIC_BYTES_PER_ROW = {1: 2114, 8: 2164}
+NCU_TRAFFIC_BYTES_PER_ROW = {1: 2109, 8: 2158}
 
 
 def measured_peaks():
