@@ -153,6 +153,11 @@ typedef struct trb_decode_args {
     int32_t     p2p_world, p2p_rank;
 } trb_decode_args_t;
 
+/* Precondition on the cache: the kernels load whole tiles (32 or 128 rows), so rows beyond the
+ * live length inside the allocation take part in the products with weight zero.  They must
+ * hold finite codes: a cache that starts zero-filled and is only written by trb_kv_append /
+ * trb_attn_prep (which never produce a NaN code) satisfies this, as the reference's State does
+ * (tokenrush/state.py:19-29); a cache made with an uninitialised allocator does not. */
 size_t trb_decode_workspace_bytes(int32_t hq, int32_t hkv, int32_t d, int32_t m);
 int    trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t *args, trb_stream_t stream);
 
