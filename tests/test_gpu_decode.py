@@ -351,14 +351,16 @@ def test_ring_wraparound_600_steps(tb):
     assert int(pos_t) == total
 
 
-def test_sequence_shards_merge_to_unsharded(tb):
+@pytest.mark.parametrize("M", [1, 4, 8])
+def test_sequence_shards_merge_to_unsharded(tb, M):
     """Two and four contiguous shards of one cache (as separate caches on this GPU): per-shard
-    partials merged by the LSE formula equal the unsharded result; the appended row lands in
-    the shard that owns its position."""
+    partials merged by the LSE formula equal the unsharded result; the appended rows land in
+    the shard that owns their positions.  M = 1 runs the mma.sync kernel, M = 4 and 8 the tcgen05
+    kernel (rows that straddle a shard boundary included: L + M crosses 1536 for M = 8 below)."""
     S = 2048                                                   # window size, sharded equally
-    L = 1500
-    kb, vb = O.seeded_bf16(71, HKV, L + 1, D), O.seeded_bf16(72, HKV, L + 1, D)
-    qb = O.seeded_bf16(73, 1, HQ, D)
+    L = 1500 if M < 8 else 1531
+    kb, vb = O.seeded_bf16(71, HKV, L + M, D), O.seeded_bf16(72, HKV, L + M, D)
+    qb = O.seeded_bf16(73, M, HQ, D)
     cfg = tb.AttnConfig(n_attn=1)
     whole = tb.State(cfg, S, "cuda", kv_dtype=F8)
     tb.fused.kv_write_prefill(to_dev(kb[:, :L]), to_dev(vb[:, :L]), whole, 0, 0)
@@ -374,15 +376,16 @@ def test_sequence_shards_merge_to_unsharded(tb):
                 tb.fused.kv_append(to_dev(kb[:, lo:hi]), to_dev(vb[:, lo:hi]), sh.k[0], sh.v[0], lo, sh.k_scale[0], sh.v_scale[0],
                                    shard_lo=sh.shard_lo)
             sh.set_pos(L)
-            tb.fused.kv_write_prefill(to_dev(kb[:, L:]), to_dev(vb[:, L:]), sh, 0, sh.pos_t)      # only the owner writes
-            ml, acc = tb.fused.attn_decode_fused(to_dev(qb).reshape(1, -1), None, sh.k[0], sh.v[0], sh.pos_t, cfg,
+            tb.fused.kv_write_prefill(to_dev(kb[:, L:]), to_dev(vb[:, L:]), sh, 0, sh.pos_t)      # only the owners write
+            ml, acc = tb.fused.attn_decode_fused(to_dev(qb).reshape(M, -1), None, sh.k[0], sh.v[0], sh.pos_t, cfg,
                                                  sh.k_scale[0], sh.v_scale[0], shard_lo=sh.shard_lo, partial=True)
             mls.append(ml); accs.append(acc)
-        owner = L // per
-        for g, sh in enumerate(shards):
-            wrote = bool((sh.k_scale[0][:, L - g * per] != 1).all()) if g == owner else False
-            assert wrote == (g == owner)
+        for t in range(M):                                     # every new row is in exactly one shard
+            owner = (L + t) // per
+            for g, sh in enumerate(shards):
+                if g * per <= L + t < (g + 1) * per:
+                    assert g == owner and bool((sh.k_scale[0][:, L + t - g * per] != 1).all())
         o = tb.fused.lse_merge(torch.stack(mls), torch.stack(accs), hq=HQ)
-        assert_attn_close(f32_of(o).reshape(1, HQ, D), f32_of(o_ref).reshape(1, HQ, D), f"G={G}")
-        assert_attn_close(f32_of(o).reshape(1, HQ, D), _oracle_step(whole, qb, L), f"G={G} vs oracle")
+        assert_attn_close(f32_of(o).reshape(M, HQ, D), f32_of(o_ref).reshape(M, HQ, D), f"M={M} G={G}")
+        assert_attn_close(f32_of(o).reshape(M, HQ, D), _oracle_step(whole, qb, L), f"M={M} G={G} vs oracle")
     assert tb._lib.device_status() == 0
