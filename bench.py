@@ -168,6 +168,37 @@ def run_product(args):
     d_q, d_k, d_v = h_q.cuda(), h_k.cuda(), h_v.cuda()
     d_out = torch.zeros(LAYERS, m, HQ * D, device="cuda", dtype=torch.bfloat16)
     launches_per_step = 0
+    # M-row verify: after the step, c ~ U{1..M} of the rows are committed on the device (drafts
+    # accepted up to the first mismatch); the rejected rows stay as dead data and the next step's
+    # append overwrites them.  The draft / prediction tokens of step s come from a seeded table that
+    # the captured graph indexes with a device counter.
+    TAB = 64
+    commit = torch.randint(1, m + 1, (TAB,), generator=torch.Generator().manual_seed(0)).tolist() if m > 1 else [1] * TAB
+    if m > 1:
+        drafts_tab = torch.arange(TAB * (m - 1), dtype=torch.int64).reshape(TAB, m - 1) % 1000
+        pred_tab = torch.cat([drafts_tab, torch.full((TAB, 1), 7, dtype=torch.int64)], 1)
+        for s_, c_ in enumerate(commit):
+            if c_ - 1 < m - 1:
+                pred_tab[s_, c_ - 1] = drafts_tab[s_, c_ - 1] + 1     # first mismatch after c - 1 accepted drafts
+        drafts_tab, pred_tab = drafts_tab.cuda(), pred_tab.cuda()
+        d_counter = torch.zeros(1, dtype=torch.int64, device="cuda")
+        d_idx = torch.zeros(1, dtype=torch.int64, device="cuda")
+        d_drafts = torch.zeros(1, m - 1, dtype=torch.int64, device="cuda")
+        d_pred = torch.zeros(1, m, dtype=torch.int64, device="cuda")
+        d_nacc = torch.zeros(1, dtype=torch.int64, device="cuda")
+        d_tok = torch.zeros(1, dtype=torch.int64, device="cuda")
+    replays = 0                                               # graph replays since the cursor was set: indexes `commit`
+
+    def live_after(n_replays):
+        """Sum of the live lengths of the next n_replays steps, advancing the host's copy of the schedule."""
+        nonlocal replays, pos_host
+        total = 0
+        for _ in range(n_replays):
+            total += pos_host + m
+            pos_host += commit[replays % TAB] if m > 1 else m
+            replays += 1
+        return total
+    pos_host = pos0
 
     def step_body(count=False):
         nonlocal launches_per_step
@@ -181,7 +212,14 @@ def run_product(args):
                 tb.fused.attn_decode_fused(d_q[l], None, state.k[l], state.v[l], state.pos_t, cfg, state.k_scale[l], state.v_scale[l],
                                            out=d_out[l])
                 n += 2                                        # append, decode (combine fused in its tail)
-        tb.fused.cursor_advance(state.pos_t, m)
+        if m > 1:
+            torch.remainder(d_counter, TAB, out=d_idx)
+            torch.index_select(drafts_tab, 0, d_idx, out=d_drafts)
+            torch.index_select(pred_tab, 0, d_idx, out=d_pred)
+            tb.fused.spec_commit(d_pred[0], d_drafts[0], d_nacc, d_tok, state.pos_t)
+            d_counter.add_(1)
+        else:
+            tb.fused.cursor_advance(state.pos_t, m)
         n += 1
         if count:
             launches_per_step = n
@@ -197,6 +235,8 @@ def run_product(args):
     with torch.cuda.graph(graph, stream=side):
         step_body()
     state.set_pos(pos0)
+    if m > 1:
+        d_counter.zero_()
 
     def barrier():
         if world > 1:
@@ -221,11 +261,10 @@ def run_product(args):
     # ---- device-resident number: K graph replays, inputs already in HBM ---------------------
     for _ in range(warmup):
         graph.replay()
+    live_after(warmup)
     with ClockSampler(local_rank) as clocks:
         ms = timed(graph.replay, steps)
-    live_first = pos0 + warmup * m + m
-    live_sum = sum(live_first + i * m for i in range(steps))
-    bytes_total = LAYERS * ROW_BYTES * live_sum
+    bytes_total = LAYERS * ROW_BYTES * live_after(steps)
     value = bytes_total / (ms * 1e-3) / 1e9
 
     # ---- end to end: pinned host inputs in, outputs back, every step ------------------------
@@ -235,9 +274,8 @@ def run_product(args):
         h_out.copy_(d_out, non_blocking=True)
         torch.cuda.current_stream().synchronize()             # the caller reads the step's result
     e2e_steps = max(10, steps // 4)
-    live_e2e_first = live_first + steps * m
     ms_e2e = timed(e2e_step, e2e_steps)
-    e2e_bytes = LAYERS * ROW_BYTES * sum(live_e2e_first + i * m for i in range(e2e_steps))
+    e2e_bytes = LAYERS * ROW_BYTES * live_after(e2e_steps)
     e2e_value = e2e_bytes / (ms_e2e * 1e-3) / 1e9
     h2d = (h_q.numel() + h_k.numel() + h_v.numel()) * 2
     d2h = h_out.numel() * 2
@@ -278,7 +316,8 @@ def run_product(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 cache, f16 MMA, fp32 softmax/accumulate" if m == 1 else "fp8_e4m3 cache and operands (q, p as hi+lo pairs), fp32 accumulate in TMEM",
             "data": "synthetic",
             "config": {"workload": args.workload, "layers": LAYERS, "context_rows": ctx, "query_rows": m,
-                       "heads": f"{HQ}q/{HKV}kv x {D}", "kv_bytes_per_step": LAYERS * ROW_BYTES * live_first,
+                       "heads": f"{HQ}q/{HKV}kv x {D}", "kv_bytes_per_step": round(bytes_total / steps),
+                       "commit": "all rows" if m == 1 else f"c ~ U{{1..{m}}} per step, seeded, on the device (trb_spec_commit)",
                        "cuda_graph": True, "cursor": "device int64", "l2": "inputs larger than L2 (no flush needed)",
                        "sharding": f"sequence x{world}" if world > 1 else "none",
                        "exchange": args.exchange if world > 1 else None},
