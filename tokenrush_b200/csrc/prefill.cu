@@ -35,8 +35,8 @@ constexpr int PF_OFF_Q = 0;                            // Qhi, Qlo
 constexpr int PF_OFF_KV = 2 * PF_Q_BYTES;              // stages of (K tile, V tile)
 constexpr int PF_OFF_P = PF_OFF_KV + PF_STAGES * 2 * PF_TILE;
 constexpr int PF_OFF_SC = PF_OFF_P + PF_P_BYTES;       // [stages][2][64] floats
-constexpr int PF_OFF_FAC = PF_OFF_SC + PF_STAGES * 2 * PF_BN * 4;   // [2][3][64] floats: per-key factors of a tile
-constexpr int PF_OFF_MX = PF_OFF_FAC + 2 * 3 * PF_BN * 4;          // [2][2][128] floats: row maxima of the two key halves
+constexpr int PF_OFF_FAC = PF_OFF_SC + PF_STAGES * 2 * PF_BN * 4;   // [3][3][64] floats: per-key factors of a tile, tiles i-1, i, i+1
+constexpr int PF_OFF_MX = PF_OFF_FAC + 3 * 3 * PF_BN * 4;          // [2][2][128] floats: row maxima of the two key halves
 constexpr int PF_OFF_BAR = PF_OFF_MX + 2 * 2 * PF_BM * 4;
 constexpr int PF_SMEM = PF_OFF_BAR + 256 + 1024;
 constexpr int PF_TMEM_COLS = 512;
@@ -212,19 +212,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         bool ok = true;
         const long long qpos_warp_min = p.pos + q0 + (warp & 3) * 32;            // lane 0's position
         const bool warp_has_padding = (warp & 3) * 32 + 31 >= rows_here;
-        for (int i = 0; i < n_tiles && ok; ++i) {
-            const int s = i % PF_STAGES, b = i & 1;
-            // per-key factors of this tile, once per CTA: score scale, log2 of the V scale, 1 / V scale
-            float *fac = sm_fac + b * 3 * PF_BN;
-            float *mxbuf = sm_mx + b * 2 * PF_BM;
-            if (!(ok = mbar_wait(&kv_full[s], (i / PF_STAGES) & 1))) break;
-            if (tid < PF_BN) {
-                const float kscv = sm_sc[(s * 2 + 0) * PF_BN + tid], vscv = sm_sc[(s * 2 + 1) * PF_BN + tid];
-                fac[tid] = kscv * p.scale_log2;
-                fac[PF_BN + tid] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
-                fac[2 * PF_BN + tid] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
+        if (n_tiles > 0) {
+            ok = mbar_wait(&kv_full[0], 0);
+            if (ok && tid < PF_BN) {
+                const float kscv = sm_sc[tid], vscv = sm_sc[PF_BN + tid];
+                sm_fac[tid] = kscv * p.scale_log2;
+                sm_fac[PF_BN + tid] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
+                sm_fac[2 * PF_BN + tid] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
             }
             named_barrier(1, PF_SOFTMAX_THREADS);
+        }
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int b = i & 1;
+            // per-key factors (score scale, log2 of the V scale, 1 / V scale), once per CTA and one tile
+            // ahead: the table of tile i+1 is written here and published by this tile's barrier below
+            float *fac = sm_fac + (i % 3) * 3 * PF_BN;
+            float *mxbuf = sm_mx + b * 2 * PF_BM;
+            if (i + 1 < n_tiles) {
+                const int s1 = (i + 1) % PF_STAGES;
+                if (!(ok = mbar_wait(&kv_full[s1], ((i + 1) / PF_STAGES) & 1))) break;
+                if (tid < PF_BN) {
+                    float *fn = sm_fac + ((i + 1) % 3) * 3 * PF_BN;
+                    const float kscv = sm_sc[(s1 * 2 + 0) * PF_BN + tid], vscv = sm_sc[(s1 * 2 + 1) * PF_BN + tid];
+                    fn[tid] = kscv * p.scale_log2;
+                    fn[PF_BN + tid] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
+                    fn[2 * PF_BN + tid] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
+                }
+            }
             if (!(ok = mbar_wait(&s_full[b], (i >> 1) & 1))) break;
             tc_fence_after();
             float sv[32];
@@ -257,6 +271,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             mt = fmaxf(mt, mxbuf[(half ^ 1) * PF_BM + row]);
             const float m_new = fmaxf(m_run, mt);
             const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+            const float m_off = m_safe - 8.f;                                   // probabilities are staged x 256
             const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run - m_safe);   // rows with no visible key yet
             // the previous PV must have landed before P is overwritten or O is corrected
             if (i > 0 && !(ok = mbar_wait(o_done, (i - 1) & 1))) break;
@@ -278,12 +293,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     const float4 fr = *reinterpret_cast<const float4 *>(fr_ + c * 16 + w * 4);
-                    const float p0 = fast_exp2(sv[c * 16 + w * 4 + 0] - m_safe), p1 = fast_exp2(sv[c * 16 + w * 4 + 1] - m_safe);
-                    const float p2 = fast_exp2(sv[c * 16 + w * 4 + 2] - m_safe), p3 = fast_exp2(sv[c * 16 + w * 4 + 3] - m_safe);
+                    const float p0 = fast_exp2(sv[c * 16 + w * 4 + 0] - m_off), p1 = fast_exp2(sv[c * 16 + w * 4 + 1] - m_off);
+                    const float p2 = fast_exp2(sv[c * 16 + w * 4 + 2] - m_off), p3 = fast_exp2(sv[c * 16 + w * 4 + 3] - m_off);
                     lsum = fmaf(p0, fr.x, lsum); lsum = fmaf(p1, fr.y, lsum); lsum = fmaf(p2, fr.z, lsum); lsum = fmaf(p3, fr.w, lsum);
                     uint32_t h01, l01, h23, l23;
-                    pf_split2_h(p0 * 256.f, p1 * 256.f, h01, l01);
-                    pf_split2_h(p2 * 256.f, p3 * 256.f, h23, l23);
+                    pf_split2_h(p0, p1, h01, l01);
+                    pf_split2_h(p2, p3, h23, l23);
                     hw[w] = h01 | (h23 << 16);
                     lw[w] = l01 | (l23 << 16);
                 }
@@ -297,14 +312,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
-        // ---- epilogue: O / (256 * l) -> bf16; l = sum of the two halves' partial sums
+        // ---- epilogue: O / l -> bf16 (both carry the factor 256); l = sum of the two halves' partial sums
         if (ok && n_tiles > 0) ok = mbar_wait(o_done, (n_tiles - 1) & 1);
         tc_fence_after();
         sm_mx[half * PF_BM + row] = l_run;
         named_barrier(1, PF_SOFTMAX_THREADS);
         const float l_tot = l_run + sm_mx[(half ^ 1) * PF_BM + row];
         if (ok) {
-            const float inv = 1.f / (l_tot * 256.f);
+            const float inv = 1.f / l_tot;
             __nv_bfloat16 *op = p.out + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D + half * (PF_D / 2);
 #pragma unroll 1
             for (int c = 0; c < PF_D / 64; ++c) {
