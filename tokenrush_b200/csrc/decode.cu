@@ -117,9 +117,10 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
     // 2. ticket.  The rows are merged by the last CTAs of this kv head to arrive, one claim (one or
     // two rows) each: arrival number `old` makes a CTA helper number old - (active - helpers), and a
     // helper takes the claims h, h + helpers, ...  Earlier arrivals leave at once and free their SM
-    // for the next kernel in the stream.  The last arrival resets the ticket (the launch replays
-    // inside a graph) and publishes a new epoch; the other helpers wait for it (bounded: a helper
-    // that gives up records TRB_ST_WAIT_TIMEOUT, its rows are then missing).
+    // for the next kernel in the stream.  The last arrival publishes a new epoch and resets the
+    // ticket (the launch replays inside a graph); the other helpers wait until the ticket shows
+    // that all splits have arrived (bounded: a helper that gives up records TRB_ST_WAIT_TIMEOUT,
+    // its rows are then missing).
     unsigned int *ticket = p.counters + j, *seq = p.counters + 128 + j;
     constexpr int ITEMS = D / 4, GROUPS = NTHREADS / ITEMS;
     const int rc = (p.rows > active && p.p2p_world == 0 && GROUPS >= 2) ? 2 : 1;     // rows per claim, see below
@@ -134,13 +135,16 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
         const unsigned int old = atomicAdd(ticket, 1u);
         int h = (int)old - (active - helpers);
         if (old == (unsigned int)(active - 1)) {
-            *ticket = 0u;                                               // ready for the next launch / replay
-            __threadfence();
             *(volatile unsigned int *)seq = epoch + 1u;
+            __threadfence();
+            *(volatile unsigned int *)ticket = 0u;                      // ready for the next launch / replay
         } else if (h >= 0) {
+            // all splits have arrived when the ticket reads `active` - or, if the last arrival has
+            // reset it already, when the epoch has moved (it is published before the reset)
             bool seen = false;
             for (int it = 0; it < (1 << 17); ++it) {
-                if (*(volatile unsigned int *)seq == epoch + 1u) { seen = true; break; }
+                const unsigned int tk = *(volatile unsigned int *)ticket, ep = *(volatile unsigned int *)seq;
+                if (tk == (unsigned int)active || ep == epoch + 1u) { seen = true; break; }
                 __nanosleep(it < 64 ? 20 : 200);
             }
             if (!seen) { raise_status(TRB_ST_WAIT_TIMEOUT); h = -1; }
