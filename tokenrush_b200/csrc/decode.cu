@@ -274,6 +274,9 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
                     const uint4 v = ld_volatile_v4(src + 2);
                     if (v.y == tag && v.w == tag) { gm = fmaxf(gm, __uint_as_float(v.x)); ok = true; break; }
                     if (it > 64) __nanosleep(100);
+                    // once a wait of this process has run out, later ones give up early: a lost peer costs
+                    // one limit, not one limit per row and layer
+                    if (it == 4096 && (*(volatile unsigned int *)&g_status & TRB_ST_PEER_TIMEOUT)) break;
                 }
             }
             // pass 2: weights and sums in rank order, own partial from registers
@@ -294,6 +297,7 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
                             break;
                         }
                         if (it > 64) __nanosleep(100);
+                        if (it == 4096 && (*(volatile unsigned int *)&g_status & TRB_ST_PEER_TIMEOUT)) break;
                     }
                 }
                 const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
