@@ -21,12 +21,12 @@
 //     (max, sum, acc) and the warps of a CTA, the CTAs of a kv head and (for sequence
 //     shards) the GPUs are all merged with the same log-sum-exp formula in a fixed order;
 //   * every CTA writes one (max, sum, acc) partial per row and takes an atomic ticket of its
-//     kv head; the last arrival resets the counters (so the launch replays inside a CUDA
-//     graph) and publishes an epoch.  The last arrivals, as many as there are output rows
-//     (or row pairs), stay (bounded wait on the epoch) and take the rows that their arrival
-//     number assigns them: a row's split partials are fetched in one round trip, merged in
-//     split order, gated if asked, and written as bf16 - or, for a sequence shard, pushed to
-//     the peers' exchange buffers and merged in rank order.
+//     kv head; the last arrival publishes an epoch and resets the ticket (so the launch
+//     replays inside a CUDA graph).  The last arrivals, as many as there are output rows (or
+//     row pairs), stay until the ticket shows that every split has arrived (bounded) and take
+//     the rows that their arrival number assigns them: a row's split partials are fetched in
+//     one round trip, merged in split order, gated if asked, and written as bf16 - or, for a
+//     sequence shard, pushed to the peers' exchange buffers and merged in rank order.
 //   * programmatic dependent launch: tiles that the preceding append cannot touch are
 //     requested before griddepcontrol.wait, so the prologue overlaps the append's tail.
 //
