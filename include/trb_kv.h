@@ -40,7 +40,9 @@ extern "C" {
 /* bits of the device status word */
 #define TRB_ST_CURSOR_RANGE   1u   /* an append / scan saw a position outside the cache   */
 #define TRB_ST_WAIT_TIMEOUT   2u   /* a bounded wait (pipeline barrier) gave up            */
-#define TRB_ST_PEER_TIMEOUT   4u   /* a bounded wait on another GPU's flag gave up         */
+#define TRB_ST_PEER_TIMEOUT   4u   /* a bounded wait on another GPU's packets gave up      */
+#define TRB_ST_WORKSPACE      8u   /* a decode workspace was not zeroed before its first use,
+                                      or two launches that share it overlapped              */
 
 #define TRB_KV_BF16 0
 #define TRB_KV_FP8  1              /* e4m3fn codes + one fp32 scale per (head, row)       */
@@ -74,11 +76,34 @@ typedef struct trb_cursor {
 int         trb_version(void);
 const char *trb_strerror(int code);
 
-/* The append / prep / decode kernels are launched with programmatic stream serialization: each
- * may start while its predecessor in the stream drains, and waits (griddepcontrol.wait) before
- * it reads anything the predecessor may have written, so results do not change.  enable = 0
- * switches to ordinary launches (also: environment variable TRB_PDL=0). */
-int trb_set_programmatic_launch(int enable);
+/* Programmatic dependent launch.  The append / prep / decode kernels are launched with
+ * programmatic stream serialization, so that a kernel may start while the launch before it
+ * drains.  What a kernel may touch before its dependency wait (griddepcontrol.wait) depends on
+ * which launches can still be running when it starts; the library works that out on the host
+ * from its own launches on the stream.  mode:
+ *   0  ordinary launches (also: environment variable TRB_PDL=0);
+ *   1  (default) every kernel waits before it releases its dependents, so only the launch
+ *      directly before a kernel can still be running.  A decode that directly follows the
+ *      append / prep of its own rows (same cache, same cursor) reads the cursor and streams the
+ *      rows below it while that append runs; every other decode waits first.  Safe with any
+ *      other work in the stream;
+ *   2  chained: appends release their dependents at once and a decode runs beside the tail of
+ *      the decode before it (its cache rows and, unless attn_prep made them, its query rows are
+ *      read before its wait; workspace, new rows and outputs after it).  The caller promises
+ *      that, between two library launches on one stream, no other work writes the caches, the
+ *      cursors or the query rows; the first library launch after any ordinary library launch
+ *      (trb_cursor_advance, trb_spec_commit, ...) or at the start of a graph capture waits
+ *      first.  Meant for a decode step captured as one graph of library calls.
+ * Results are the same in all modes.  Returns TRB_E_ARG for another value. */
+int trb_set_programmatic_launch(int mode);
+
+/* Poll limits of the bounded device-side waits on the current device (0 restores a default):
+ * pipeline_polls - shared-memory pipeline barriers (default 2^20, about a second);
+ * tail_polls     - split partials in the decode tail (default 2^17);
+ * peer_polls     - packets of another GPU in the fused exchange (default 2^22).
+ * A wait that runs out sets TRB_ST_WAIT_TIMEOUT or TRB_ST_PEER_TIMEOUT, the kernel returns and
+ * the call's output is undefined; nothing hangs.  Synchronises the device: set-up time only. */
+int trb_set_wait_limits(uint32_t pipeline_polls, uint32_t tail_polls, uint32_t peer_polls);
 
 /* trb_attn_decode has two kernels for FP8 caches of head dim 256 without ring or window: a
  * mma.sync kernel (any M; the bandwidth kernel for M = 1) and a tcgen05 kernel that keeps the
@@ -137,14 +162,16 @@ typedef struct trb_decode_args {
     const float *extra_acc;      /* [m*hq, n_extra, d]                                      */
     trb_cursor_t pos;
     void       *workspace;       /* trb_decode_workspace_bytes() bytes, zeroed once before
-                                    the first use; calls that share it must be stream-ordered */
+                                    the first use (and again after a call that reported
+                                    TRB_ST_WAIT_TIMEOUT / TRB_ST_WORKSPACE); calls that share
+                                    it must be ordered on one stream                         */
     size_t      workspace_bytes;
     /* sequence shards over several GPUs: when partial_out is set the tail writes this
      * GPU's merged partial (max, sum, unnormalised acc) instead of out               */
     float      *partial_ml;      /* [m*hq, 2]                                               */
     float      *partial_acc;     /* [m*hq, d]                                               */
     /* ... or, fused: when p2p_xchg is set (and p2p_world > 1) the tail exchanges the partials
-     * with the other GPUs itself (peer stores + flags, bounded wait, rank-order merge) and
+     * with the other GPUs itself (tagged peer stores, bounded wait, rank-order merge) and
      * writes the final out on every GPU.  p2p_xchg: HOST array of p2p_world device pointers to the
      * GPUs' exchange buffers (trb_p2p_exchange_bytes(world, m*hq, d) bytes each, from
      * trb_p2p_create / trb_p2p_open).  All GPUs must make the same sequence of decode calls on
@@ -168,22 +195,26 @@ int    trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t *args, 
  * For callers that cannot give the library device memory at the point of the call: a host
  * runtime whose device memory belongs to its own arena and has no allocation hook for plugins,
  * or a thin FFI binding that only forwards the buffers it received and has no way to create
- * one more.  Same arguments and result as
- * trb_attn_decode, except that args->workspace / workspace_bytes are ignored: the split
- * partials and tickets live in a file-scope device array of TRB_STATIC_SCRATCH_BYTES that is
- * part of the library image (every GPU that loads the library holds it until the process
- * exits).  The call itself allocates and frees nothing.
+ * one more.  Same arguments and result as trb_attn_decode, except that args->workspace /
+ * workspace_bytes are ignored: the split partials and ticket words live in a file-scope device
+ * array of TRB_STATIC_SCRATCH_BYTES that is part of the library image (every GPU that loads the
+ * library holds it until the process exits).  The call itself allocates and frees nothing.
  *
  *   - Limit: the scratch need of the geometry, trb_decode_workspace_bytes(hq, hkv, d, m), must
- *     not exceed TRB_STATIC_SCRATCH_BYTES (4 MiB: up to m = 4 rows for 24 query / 4 KV heads
+ *     not exceed TRB_STATIC_SCRATCH_BYTES (8 MiB: up to m = 4 rows for 24 query / 4 KV heads
  *     x 256); larger calls return TRB_E_SCRATCH_LIMIT and launch nothing.
+ *   - args->p2p_xchg must be NULL (TRB_E_UNSUPPORTED otherwise): the exchange between GPUs is
+ *     tagged with the launch count of the workspace, which all GPUs must agree on, and this
+ *     array is shared by every caller in the process.
  *   - The first call on each device looks up the array's device address (with that device
  *     current) and keeps it; make that first call before any stream capture begins.
- *   - All calls share the one array, which keeps the previous call's contents; the call clears
- *     the small header that must start at zero (stream-ordered) and every partial is rewritten
- *     before it is read.  Two calls whose kernels overlap on the GPU (different streams, or
- *     several host threads) race on it: order them on one stream. */
-#define TRB_STATIC_SCRATCH_BYTES (4u << 20)
+ *   - All calls share the one array, which keeps the previous call's contents.  Before its
+ *     kernel, each call zeroes the arrival counts in the array's header and advances the tag
+ *     that marks this call's partials (one tiny launch, stream-ordered); partials are
+ *     recognised by that tag, so nothing else needs clearing.  Two calls whose kernels overlap
+ *     on the GPU (different streams, or several host threads) race on the array: order them on
+ *     one stream. */
+#define TRB_STATIC_SCRATCH_BYTES (8u << 20)
 #define TRB_E_SCRATCH_LIMIT (-7)
 int trb_attn_decode_static(const trb_cache_t *cache, const trb_decode_args_t *args, trb_stream_t stream);
 

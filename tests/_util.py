@@ -51,3 +51,29 @@ def oracle_state_from(state, slot=0) -> O.OracleState:
         st.k[0] = bits_of(state.k[slot])
         st.v[0] = bits_of(state.v[slot])
     return st
+
+
+def fill_cache_gpu(tb, state, slot: int, rows: int, seed: int, start: int = 0, chunk: int = 16384):
+    """Rows [start, start + rows) of one layer <- N(0,1) bf16 drawn on the GPU and written by the
+    product's own append (the oracle later reads the bytes back, so the CPU never has to quantise
+    hundreds of thousands of rows)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    hkv, _, d = state.k[slot].shape
+    ks, vs = (state.k_scale[slot], state.v_scale[slot]) if state.fp8 else (None, None)
+    for p0 in range(start, start + rows, chunk):
+        t = min(chunk, start + rows - p0)
+        k = torch.randn(hkv, t, d, device="cuda", generator=g).to(torch.bfloat16)
+        v = torch.randn(hkv, t, d, device="cuda", generator=g).to(torch.bfloat16)
+        tb.fused.kv_append(k, v, state.k[slot], state.v[slot], p0, ks, vs)
+    torch.cuda.synchronize()
+
+
+def rows_bit_exact(state, slot: int, pos: int, k_bits: np.ndarray, v_bits: np.ndarray):
+    """The codes and scales of cache rows pos.. equal what the oracle's quantiser makes of the bf16 rows."""
+    t = k_bits.shape[1]
+    for src, cache, scale, what in ((k_bits, state.k, state.k_scale, "K"), (v_bits, state.v, state.v_scale, "V")):
+        codes, sc = O.quantize_rows(O.bf16_bits_to_f32(src))
+        got_c = cache[slot][:, pos:pos + t].view(torch.uint8).cpu().numpy()
+        got_s = scale[slot][:, pos:pos + t].cpu().numpy()
+        assert np.array_equal(got_c, codes), f"{what} codes differ"
+        assert np.array_equal(got_s.view(np.uint32), sc.view(np.uint32)), f"{what} scales differ"

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("TRB_KV_LIB") or os.path.join(HERE, "libtrb_kv.so")
 
 TRB_KV_BF16, TRB_KV_FP8 = 0, 1
-ST_CURSOR_RANGE, ST_WAIT_TIMEOUT, ST_PEER_TIMEOUT = 1, 2, 4
+ST_CURSOR_RANGE, ST_WAIT_TIMEOUT, ST_PEER_TIMEOUT, ST_WORKSPACE = 1, 2, 4, 8
 IPC_HANDLE_BYTES = 64
 
 
@@ -56,6 +56,7 @@ SIGNATURES = {
     "trb_version": (C.c_int, []),
     "trb_strerror": (C.c_char_p, [C.c_int]),
     "trb_set_programmatic_launch": (C.c_int, [C.c_int]),
+    "trb_set_wait_limits": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32]),
     "trb_set_decode_tensor_rows": (C.c_int, [C.c_int32]),
     "trb_device_status": (C.c_int, [C.POINTER(C.c_uint32)]),
     "trb_kv_append": (C.c_int, [C.POINTER(Cache), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,

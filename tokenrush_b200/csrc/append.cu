@@ -96,11 +96,14 @@ __device__ __forceinline__ void load_row(const __nv_bfloat16 *src, int lane, flo
 template <int D>
 __global__ void __launch_bounds__(32) kv_append_kernel(CacheView c, const __nv_bfloat16 *k_src, const __nv_bfloat16 *v_src,
                                                        long long head_stride, long long row_stride, Cursor pos, Cursor n_valid,
-                                                       int has_valid) {
+                                                       int has_valid, int trigger_top) {
     constexpr int EPT = D / 32;
     const int i = blockIdx.x, head = blockIdx.y, which = blockIdx.z, lane = threadIdx.x;
-    pdl_launch_dependents();          // the decode that follows may start streaming old rows now
-    pdl_wait();                       // ... while this kernel waits for whatever produced its inputs
+    // Inside a chain of library launches the decode that follows may start streaming the rows
+    // below the cursor at once; otherwise it starts once everything before this launch is complete.
+    if (trigger_top) pdl_launch_dependents();
+    pdl_wait();                       // whatever produced the inputs, and every earlier launch, is complete
+    if (!trigger_top) pdl_launch_dependents();
     if (has_valid && i >= load_cursor(n_valid)) return;
     const long long p = load_cursor(pos) + i;
     const long long row = row_of_position(c, p);
@@ -123,7 +126,7 @@ template <int D>
 __global__ void __launch_bounds__(32) attn_prep_kernel(CacheView c, const __nv_bfloat16 *qkv, const __nv_bfloat16 *qw,
                                                        const __nv_bfloat16 *kw, const __nv_bfloat16 *cos_t,
                                                        const __nv_bfloat16 *sin_t, long long table_rows, int rd, float eps,
-                                                       int hq, Cursor pos, __nv_bfloat16 *q_out) {
+                                                       int hq, Cursor pos, __nv_bfloat16 *q_out, int trigger_top) {
     constexpr int EPT = D / 32;
     const int head = blockIdx.x, i = blockIdx.y, lane = threadIdx.x;
     const long long qkv_w = (long long)hq * 2 * D + 2LL * c.hkv * D;
@@ -131,8 +134,9 @@ __global__ void __launch_bounds__(32) attn_prep_kernel(CacheView c, const __nv_b
     const int j = head - hq;
     const __nv_bfloat16 *src = qkv + i * qkv_w + (is_q ? (long long)head * 2 * D : (long long)hq * 2 * D + (long long)j * D);
     const __nv_bfloat16 *w = is_q ? qw : kw;
-    pdl_launch_dependents();
+    if (trigger_top) pdl_launch_dependents();
     pdl_wait();
+    if (!trigger_top) pdl_launch_dependents();
     const long long p = load_cursor(pos) + i;
 
     float x[EPT];
@@ -246,9 +250,10 @@ extern "C" int trb_kv_append(const trb_cache_t *cache, const void *k_src, const 
     Cursor pc = make_cursor(pos), nv = make_cursor(n_valid);
     cudaStream_t st = (cudaStream_t)stream;
     const int hv = n_valid != nullptr;
+    const int plan = pdl_plan_writer(st, c.k, pos, WrittenRange{nullptr, 0});
     TRB_CUDA_CHECK(launch_kernel(c.d == 256 ? kv_append_kernel<256> : kv_append_kernel<128>, grid, dim3(32), 0, st, true, c,
                                  (const __nv_bfloat16 *)k_src, (const __nv_bfloat16 *)v_src, (long long)src_head_stride,
-                                 (long long)src_row_stride, pc, nv, hv));
+                                 (long long)src_row_stride, pc, nv, hv, (plan & PDL_TRIGGER_TOP) ? 1 : 0));
     return TRB_OK;
 }
 
@@ -266,10 +271,11 @@ extern "C" int trb_attn_prep(const trb_cache_t *cache, const void *qkv, const vo
     dim3 grid(hq + c.hkv, m);
     Cursor pc = make_cursor(pos);
     cudaStream_t st = (cudaStream_t)stream;
+    const int plan = pdl_plan_writer(st, c.k, pos, WrittenRange{q_out, (size_t)m * hq * c.d * sizeof(__nv_bfloat16)});
     TRB_CUDA_CHECK(launch_kernel(c.d == 256 ? attn_prep_kernel<256> : attn_prep_kernel<128>, grid, dim3(32), 0, st, true, c,
                                  (const __nv_bfloat16 *)qkv, (const __nv_bfloat16 *)q_norm_w, (const __nv_bfloat16 *)k_norm_w,
                                  (const __nv_bfloat16 *)cos, (const __nv_bfloat16 *)sin, (long long)table_rows, (int)rotary_dim, eps,
-                                 (int)hq, pc, (__nv_bfloat16 *)q_out));
+                                 (int)hq, pc, (__nv_bfloat16 *)q_out, (plan & PDL_TRIGGER_TOP) ? 1 : 0));
     return TRB_OK;
 }
 
@@ -277,6 +283,7 @@ extern "C" int trb_spec_commit(const int64_t *pred, const int64_t *drafts, int32
                                void *pos, int32_t pos_width, trb_stream_t stream) {
     if (!pred || !drafts || k < 0 || k > 64) return TRB_E_ARG;
     if (pos && pos_width != 4 && pos_width != 8) return TRB_E_ARG;
+    pdl_note_fence((cudaStream_t)stream);
     spec_commit_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const long long *)pred, (const long long *)drafts, k,
                                                            (long long *)n_accepted, (long long *)tok, pos, pos_width);
     TRB_CUDA_CHECK(cudaGetLastError());
@@ -285,6 +292,7 @@ extern "C" int trb_spec_commit(const int64_t *pred, const int64_t *drafts, int32
 
 extern "C" int trb_cursor_advance(void *pos, int32_t pos_width, int64_t delta, trb_stream_t stream) {
     if (!pos || (pos_width != 4 && pos_width != 8)) return TRB_E_ARG;
+    pdl_note_fence((cudaStream_t)stream);
     cursor_advance_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pos, pos_width, delta);
     TRB_CUDA_CHECK(cudaGetLastError());
     return TRB_OK;

@@ -75,10 +75,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after 2^20 polls (about a second), records TRB_ST_WAIT_TIMEOUT and
-// returns false so that the caller can leave its loop instead of hanging the GPU.
+// Poll limits of the bounded waits, per device, set by trb_set_wait_limits():
+//   [0] pipeline barriers (mbarrier polls, about a second by default),
+//   [1] split partials in the decode tail,  [2] packets of another GPU.
+__constant__ unsigned int c_wait_limit[3] = {1u << 20, 1u << 17, 1u << 22};
+
+// Bounded wait: gives up after c_wait_limit[0] polls, records TRB_ST_WAIT_TIMEOUT and returns
+// false so that the caller can leave its loop instead of hanging the GPU.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    for (uint32_t it = 0; it < (1u << 20); ++it) {
+    const uint32_t limit = c_wait_limit[0];
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (it > 64) __nanosleep(64);
     }
@@ -168,8 +174,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // Programmatic dependent launch: a kernel launched with the attribute may start while its
 // predecessor in the stream is still running.  It must execute pdl_wait() before it reads
-// anything the predecessor wrote; pdl_launch_dependents() lets its own successor start.  Both
-// are no-ops for a kernel launched the ordinary way.
+// anything that a launch still in flight may have written; pdl_launch_dependents() lets its own
+// successor start.  Both are no-ops for a kernel launched the ordinary way.  Which launches can
+// still be in flight when a kernel starts is worked out on the host (PdlPlan below).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -178,8 +185,35 @@ __device__ __forceinline__ void named_barrier(int id, int threads) {
 }
 
 
+// ---- host-side plan of a launch under programmatic dependent launch ----------------------------
+// A kernel that triggers its dependents before its own wait lets them run beside everything that
+// is still in flight before it, so what a kernel may touch before its wait depends on the
+// launches that precede it in the stream.  The library keeps, per stream, the list of its own
+// launches since the last point at which everything earlier was known to be complete, and
+// derives the flags below from it.  Modes (trb_set_programmatic_launch):
+//   0  ordinary launches;
+//   1  every kernel waits before it triggers, so only the direct predecessor can be in flight;
+//   2  "chained": appends and decodes trigger at their top; the caller promises that between
+//      two library launches on a stream nothing else writes the caches, cursors or queries.
+enum PdlFlags : int {
+    PDL_PRE_CURSOR = 1,    // decode: the cursor and the rows below the in-flight append are complete
+    PDL_ALL_STABLE = 2,    // decode: no launch in flight writes this cache: every live row is complete
+    PDL_PRE_Q = 4,         // decode: the query rows are complete
+    PDL_TRIGGER_TOP = 8,   // trigger the dependents before the first wait
+    PDL_WAIT_FIRST = 16,   // append / prep: wait, then trigger
+};
+struct WrittenRange { const void *lo; size_t bytes; };
+int pdl_mode();
+// a launch that writes rows of `cache_k` at `pos`.. (and `extra`, the q_out of attn_prep)
+int pdl_plan_writer(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, WrittenRange extra);
+// a decode of `cache_k` at `pos` reading `q`, writing `out[0..2]`
+int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, int new_rows, WrittenRange q,
+                    const WrittenRange (&out)[3]);
+// an ordinary launch of the library on `st`: everything before it completes before anything after it starts
+void pdl_note_fence(cudaStream_t st);
+
 // Host: launch with (or without) the programmatic-stream-serialization attribute.
-bool pdl_enabled();
+inline bool pdl_enabled() { return pdl_mode() != 0; }
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args &&...args) {
     cudaLaunchConfig_t cfg = {};

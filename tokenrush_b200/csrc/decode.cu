@@ -63,8 +63,10 @@ struct DecodeParams {
     Cursor pos;
     long long max_len, ring, shard_lo;
     int sharded;
-    unsigned int *counters;       // [3][64]: tickets, slice claims, launch epochs (per kv head)
-    float *part_ml, *part_acc;
+    int pdl_flags;                // PDL_*: what this launch may touch before its dependency wait
+    unsigned long long *word;     // [hkv] ticket words: launch epoch << 16 | CTAs arrived
+    uint4 *part_ml;               // [hkv][nsplit][rows_pad] (max, tag, sum, tag)
+    uint2 *part_acc;              // [hkv][nsplit][rows_pad][D] (value, tag)
     float *shard_ml, *shard_acc;
     void *p2p_ptr[8];             // sequence shards: every GPU's exchange buffer as mapped here
     int p2p_world, p2p_rank;      // p2p_world == 0: no exchange
@@ -107,61 +109,76 @@ __device__ __forceinline__ int acc_dim(int a, int i, int g) {
     return 16 * a + 8 * (i >> 1) + g;
 }
 
-// Ticket and tail shared by the decode kernels.  Called by every thread of the CTA once the
-// CTA's partial (max, sum, acc) rows are written to the workspace.  `smem` is scratch from its
-// start (at least 16 KB), `sm_flag` three ints outside that scratch.
-template <int D, int NTHREADS>
-__device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem, int *sm_flag, const int j, const int active,
-                                            const unsigned int epoch) {
-    const int tid = threadIdx.x, lane = threadIdx.x & 31;
-    // 2. ticket.  The rows are merged by the last CTAs of this kv head to arrive, one claim (one or
-    // two rows) each: arrival number `old` makes a CTA helper number old - (active - helpers), and a
-    // helper takes the claims h, h + helpers, ...  Earlier arrivals leave at once and free their SM
-    // for the next kernel in the stream.  The last arrival publishes a new epoch and resets the
-    // ticket (the launch replays inside a graph); the other helpers wait until the ticket shows
-    // that all splits have arrived (bounded: a helper that gives up records TRB_ST_WAIT_TIMEOUT,
-    // its rows are then missing).
-    unsigned int *ticket = p.counters + j, *seq = p.counters + 128 + j;
-    constexpr int ITEMS = D / 4, GROUPS = NTHREADS / ITEMS;
-    const int rc = (p.rows > active && p.p2p_world == 0 && GROUPS >= 2) ? 2 : 1;     // rows per claim, see below
+// ---- ticket, partials and tail shared by the decode kernels ------------------------------------
+// Every CTA of a kv head publishes one (max, sum, acc) partial per query row in the workspace and
+// the last CTAs to arrive merge them.  Nothing in this exchange is ordered by a fence or a flag:
+// every 8 bytes of a partial are a (value, tag) pair, the tag being the launch's epoch + 1, and a
+// reader polls the data itself until the tags are those of its own launch (bounded).  The epoch
+// and the arrival number of a CTA come from ONE atomic on the kv head's ticket word
+// (epoch << 16 | arrived): the CTA that completes the count adds what makes the count zero and
+// the epoch one more, so the word is ready for the next launch on this workspace (which touches
+// it only after its dependency wait, i.e. after this launch has completed).
+
+// Both called by one thread of the CTA, after the dependency wait: the first issues the atomic,
+// the second (as late as the caller can afford, the round trip runs in between) turns its result
+// into sm_flag[0] <- helper number of this CTA (or -1: not a helper), sm_flag[2] <- epoch.
+__device__ __forceinline__ unsigned long long decode_ticket_take(const DecodeParams &p, const int j) {
+    return atomicAdd(p.word + j, 1ull);
+}
+__device__ __forceinline__ void decode_ticket(const DecodeParams &p, const int j, const int active, const int groups, int *sm_flag,
+                                              const unsigned long long old) {
+    const unsigned int arrival = (unsigned int)(old & 0xffffull);
+    if (arrival == (unsigned int)(active - 1)) atomicAdd(p.word + j, (1ull << 16) - (unsigned long long)active);
+    // More arrivals than splits: the word was not zeroed, or two launches overlap on one workspace.
+    if (arrival >= (unsigned int)active) raise_status(TRB_ST_WORKSPACE);
+    const int rc = (p.rows > active && p.p2p_world == 0 && groups >= 2) ? 2 : 1;     // rows per claim
     const int nclaims = (p.rows + rc - 1) / rc;
     const int helpers = nclaims < active ? nclaims : active;
-    // release / acquire through one thread: the barrier orders the CTA's partial stores before
-    // thread 0's fence, the fence makes them visible before the ticket; on the way back the fence
-    // after the epoch was seen comes before the barrier that lets the other threads load
-    __syncthreads();
-    if (tid == 0) {
-        __threadfence();
-        const unsigned int old = atomicAdd(ticket, 1u);
-        int h = (int)old - (active - helpers);
-        if (old == (unsigned int)(active - 1)) {
-            *(volatile unsigned int *)seq = epoch + 1u;
-            __threadfence();
-            *(volatile unsigned int *)ticket = 0u;                      // ready for the next launch / replay
-        } else if (h >= 0) {
-            // all splits have arrived when the ticket reads `active` - or, if the last arrival has
-            // reset it already, when the epoch has moved (it is published before the reset)
-            bool seen = false;
-            for (int it = 0; it < (1 << 17); ++it) {
-                const unsigned int tk = *(volatile unsigned int *)ticket, ep = *(volatile unsigned int *)seq;
-                if (tk == (unsigned int)active || ep == epoch + 1u) { seen = true; break; }
-                __nanosleep(it < 64 ? 20 : 200);
-            }
-            if (!seen) { raise_status(TRB_ST_WAIT_TIMEOUT); h = -1; }
-        }
-        __threadfence();
-        *sm_flag = h;
-        sm_flag[2] = (int)epoch;
-    }
-    __syncthreads();
-    const int helper = *sm_flag;
-    if (helper < 0) return;
+    // the rows are merged by the last CTAs of this kv head to arrive, one claim (one or two rows) at a
+    // time: arrival number a makes a CTA helper a - (active - helpers); earlier arrivals leave after
+    // writing their partial and free their SM for the next kernel in the stream
+    const int h = (int)arrival - (active - helpers);
+    sm_flag[0] = (h >= 0 && h < helpers) ? h : -1;
+    sm_flag[2] = (int)(unsigned int)(old >> 16);
+}
 
-    // 3. tail: LSE merge of the output rows over the active splits (+ extra partials), in split
-    // order: thread (item, group) sums the splits of its group, the groups are added in group
-    // order through shared memory.  With more rows than splits (M-row verify) a claim takes two
-    // rows and the thread groups form two teams, one per row, so that one round of claims covers
-    // all rows.
+__device__ __forceinline__ void st_tagged4(uint2 *dst, const float4 v, const unsigned int tag) {
+    st_volatile_v4(reinterpret_cast<uint4 *>(dst), make_uint4(__float_as_uint(v.x), tag, __float_as_uint(v.y), tag));
+    st_volatile_v4(reinterpret_cast<uint4 *>(dst) + 1, make_uint4(__float_as_uint(v.z), tag, __float_as_uint(v.w), tag));
+}
+
+// Poll a (value, tag, value, tag) packet until both tags are `tag`; false after the limit (or,
+// once a wait of this process has run out, after a short while: one stale workspace costs one
+// limit, not one per row).
+__device__ __forceinline__ bool poll_tagged(const uint4 *src, const unsigned int tag, uint4 &v, const unsigned int limit) {
+    for (unsigned int it = 0; it < limit; ++it) {
+        if (v.y == tag && v.w == tag) return true;
+        if (it > 16) __nanosleep(it < 256 ? 40 : 200);
+        if (it == 2048 && (*(volatile unsigned int *)&g_status & TRB_ST_WAIT_TIMEOUT)) break;
+        v = ld_volatile_v4(src);
+    }
+    return v.y == tag && v.w == tag;
+}
+
+// Tail: LSE merge of the output rows over the active splits (+ extra partials), in split order,
+// by the helper CTAs.  Called by every thread of the CTA after the CTA's own partial rows are
+// on their way to the workspace and sm_flag is visible.  `smem` is scratch from its start (at
+// least 16 KB) once every thread has passed the barrier below.
+template <int D, int NTHREADS>
+__device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem, const int *sm_flag, const int j, const int active) {
+    const int helper = sm_flag[0];
+    if (helper < 0) return;
+    const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
+    const int tid = threadIdx.x, lane = threadIdx.x & 31;
+    constexpr int ITEMS = D / 4, GROUPS = NTHREADS / ITEMS;
+    const int rc = (p.rows > active && p.p2p_world == 0 && GROUPS >= 2) ? 2 : 1;     // as in decode_ticket
+    const int nclaims = (p.rows + rc - 1) / rc;
+    const int helpers = nclaims < active ? nclaims : active;
+    const unsigned int limit = c_wait_limit[1];
+
+    // Thread (item, group) sums the splits of its group, the groups are added in group order
+    // through shared memory.  With more rows than splits (M-row verify) a claim takes two rows and
+    // the thread groups form two teams, one per row, so that one round of claims covers all rows.
     const int n_parts = active + p.n_extra;
     const int gt = GROUPS / rc;                                         // groups per team
     const int item = tid % ITEMS, grp = tid / ITEMS, d4 = item * 4;
@@ -172,28 +189,36 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
     float *sm_l = sm_m + (DEC_MAX_SPLITS + 4);                          // [n_parts]
     float4 *sm_red = reinterpret_cast<float4 *>(reinterpret_cast<float *>(smem) + 4 * (DEC_MAX_SPLITS + 4)) +
                      (in_team ? team : 0) * gt * ITEMS;                 // [gt][ITEMS] per team
+    constexpr int PRE = 8;                                              // splits per thread requested together
+    bool all_ok = true;
     for (int c = helper; c < nclaims; c += helpers) {
-        if (c != helper) __syncthreads();                               // the scratch of the previous claim is free
+        __syncthreads();                                                // the shared memory below is free (first claim: the CTA's own partial has left it)
         const int row = c * rc + team;
         const bool row_on = in_team && row < p.rows;
         const int qi = row_on ? row / p.g : 0, hq = row_on ? j * p.g + row % p.g : 0;
         const long long grow = (long long)qi * p.hq + hq;
         // one round trip: the (max, sum) pairs of all splits and this thread's first slices of the
-        // accumulators are requested together; the weights are applied once both are here
-        const float *pa = p.part_acc + ((long long)j * p.nsplit * p.rows_pad + (row_on ? row : 0)) * D + d4;
-        const long long pstride = (long long)p.rows_pad * D;
-        constexpr int PRE = 13;
-        float4 pre[PRE];
+        // accumulators are requested together; whatever has not arrived yet is polled afterwards
+        const uint4 *pa = reinterpret_cast<const uint4 *>(p.part_acc + ((long long)j * p.nsplit * p.rows_pad + (row_on ? row : 0)) * D + d4);
+        const long long pstride = (long long)p.rows_pad * D / 2;        // uint4 (two pairs) per split
+        uint4 a0[PRE], a1[PRE];
 #pragma unroll
         for (int u = 0; u < PRE; ++u) {
             const int sp = tgrp + u * gt;
-            pre[u] = (row_on && sp < active) ? __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row_on && sp < active) { a0[u] = ld_volatile_v4(pa + sp * pstride); a1[u] = ld_volatile_v4(pa + sp * pstride + 1); }
+            else { a0[u] = make_uint4(0u, tag, 0u, tag); a1[u] = a0[u]; }
         }
         if (row_on)
             for (int sp = ttid; sp < n_parts; sp += team_threads) {
                 float2 v;
-                if (sp < active) v = __ldcg(reinterpret_cast<const float2 *>(&p.part_ml[(((long long)j * p.nsplit + sp) * p.rows_pad + row) * 2]));
-                else v = *reinterpret_cast<const float2 *>(&p.extra_ml[(grow * p.n_extra + (sp - active)) * 2]);
+                if (sp < active) {
+                    const uint4 *src = p.part_ml + ((long long)j * p.nsplit + sp) * p.rows_pad + row;
+                    uint4 w = ld_volatile_v4(src);
+                    if (!poll_tagged(src, tag, w, limit)) { all_ok = false; w.x = __float_as_uint(-INFINITY); w.z = 0u; }
+                    v = make_float2(__uint_as_float(w.x), __uint_as_float(w.z));
+                } else {
+                    v = *reinterpret_cast<const float2 *>(&p.extra_ml[(grow * p.n_extra + (sp - active)) * 2]);
+                }
                 sm_m[sp] = v.x; sm_l[sp] = v.y;
             }
         __syncthreads();
@@ -204,19 +229,25 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
             mmax = warp_max(mmax);
             for (int sp = lane; sp < n_parts; sp += 32) lsum += sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax) * sm_l[sp];
             lsum = warp_sum(lsum);
+            for (int sp0 = tgrp; sp0 < active; sp0 += PRE * gt) {         // split order within the group: ascending
+                if (sp0 != tgrp) {
 #pragma unroll
-            for (int u = 0; u < PRE; ++u) {                                // split order within the group: ascending
-                const int sp = tgrp + u * gt;
-                if (sp < active) {
-                    const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
-                    o.x = fmaf(w, pre[u].x, o.x); o.y = fmaf(w, pre[u].y, o.y); o.z = fmaf(w, pre[u].z, o.z); o.w = fmaf(w, pre[u].w, o.w);
+                    for (int u = 0; u < PRE; ++u) {
+                        const int sp = sp0 + u * gt;
+                        if (sp < active) { a0[u] = ld_volatile_v4(pa + sp * pstride); a1[u] = ld_volatile_v4(pa + sp * pstride + 1); }
+                    }
                 }
-            }
-#pragma unroll 4
-            for (int sp = tgrp + PRE * gt; sp < active; sp += gt) {
-                const float4 v = __ldcg(reinterpret_cast<const float4 *>(pa + sp * pstride));
-                const float w = sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax);
-                o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+#pragma unroll
+                for (int u = 0; u < PRE; ++u) {
+                    const int sp = sp0 + u * gt;
+                    if (sp < active) {
+                        const bool here = poll_tagged(pa + sp * pstride, tag, a0[u], limit) && poll_tagged(pa + sp * pstride + 1, tag, a1[u], limit);
+                        if (!here) all_ok = false;
+                        const float w = (sm_m[sp] == -INFINITY || !here) ? 0.f : fast_exp2(sm_m[sp] - mmax);
+                        o.x = fmaf(w, __uint_as_float(a0[u].x), o.x); o.y = fmaf(w, __uint_as_float(a0[u].z), o.y);
+                        o.z = fmaf(w, __uint_as_float(a1[u].x), o.z); o.w = fmaf(w, __uint_as_float(a1[u].z), o.w);
+                    }
+                }
             }
             if (tgrp == 0)
                 for (int e = 0; e < p.n_extra; ++e) {
@@ -250,7 +281,6 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
             // (a GPU cannot be more than one call ahead of a peer whose packets it waits for).  This
             // GPU's own partial stays in registers.
             const P2PLayout xl = p2p_layout(p.p2p_world, p.m * p.hq, D);
-            const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
             const size_t slot = tag % P2P_SLOTS;
             const size_t nrow = (size_t)(p.m * p.hq);
             const uint4 k0 = make_uint4(__float_as_uint(o.x), tag, __float_as_uint(o.y), tag);
@@ -263,49 +293,53 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
                 st_volatile_v4(dst, k0); st_volatile_v4(dst + 1, k1); st_volatile_v4(dst + 2, k2);
             }
             const uint4 *local = reinterpret_cast<const uint4 *>((const uint8_t *)p.p2p_ptr[p.p2p_rank] + xl.ll);
-            // pass 1: the peers' maxima (their third packet)
-            float gm = mmax;
-            bool ok = true;
-            for (int r = 0; r < p.p2p_world && ok; ++r) {
-                if (r == p.p2p_rank) continue;
-                const uint4 *src = local + (((slot * p.p2p_world + r) * nrow + grow) * ITEMS + item) * 3;
-                ok = false;
-                for (unsigned int it = 0; it < P2P_SPIN_LIMIT; ++it) {
-                    const uint4 v = ld_volatile_v4(src + 2);
-                    if (v.y == tag && v.w == tag) { gm = fmaxf(gm, __uint_as_float(v.x)); ok = true; break; }
-                    if (it > 64) __nanosleep(100);
-                    // once a wait of this process has run out, later ones give up early: a lost peer costs
-                    // one limit, not one limit per row and layer
-                    if (it == 4096 && (*(volatile unsigned int *)&g_status & TRB_ST_PEER_TIMEOUT)) break;
-                }
-            }
-            // pass 2: weights and sums in rank order, own partial from registers
-            float gl = 0.f;
-            float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int r = 0; r < p.p2p_world && ok; ++r) {
-                float2 mlr = make_float2(mmax, lsum);
-                float4 v = o;
-                if (r != p.p2p_rank) {
+            // one polling loop over all peers: a peer's three packets are taken when all six tags match
+            const unsigned int plimit = c_wait_limit[2];
+            uint4 pk[P2P_MAX_WORLD][3];
+            unsigned int pending = 0u;
+            for (int r = 0; r < p.p2p_world; ++r)
+                if (r != p.p2p_rank) pending |= 1u << r;
+            for (unsigned int it = 0; it < plimit && pending; ++it) {
+#pragma unroll
+                for (int r = 0; r < P2P_MAX_WORLD; ++r) {
+                    if (!((pending >> r) & 1u)) continue;
                     const uint4 *src = local + (((slot * p.p2p_world + r) * nrow + grow) * ITEMS + item) * 3;
-                    ok = false;
-                    for (unsigned int it = 0; it < P2P_SPIN_LIMIT; ++it) {
-                        const uint4 a0 = ld_volatile_v4(src), a1 = ld_volatile_v4(src + 1), a2 = ld_volatile_v4(src + 2);
-                        if (a0.y == tag && a0.w == tag && a1.y == tag && a1.w == tag && a2.y == tag && a2.w == tag) {
-                            v = make_float4(__uint_as_float(a0.x), __uint_as_float(a0.z), __uint_as_float(a1.x), __uint_as_float(a1.z));
-                            mlr = make_float2(__uint_as_float(a2.x), __uint_as_float(a2.z));
-                            ok = true;
-                            break;
-                        }
-                        if (it > 64) __nanosleep(100);
-                        if (it == 4096 && (*(volatile unsigned int *)&g_status & TRB_ST_PEER_TIMEOUT)) break;
+                    const uint4 b0 = ld_volatile_v4(src), b1 = ld_volatile_v4(src + 1), b2 = ld_volatile_v4(src + 2);
+                    if (b0.y == tag && b0.w == tag && b1.y == tag && b1.w == tag && b2.y == tag && b2.w == tag) {
+                        pk[r][0] = b0; pk[r][1] = b1; pk[r][2] = b2;
+                        pending &= ~(1u << r);
                     }
                 }
-                const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
-                gl = fmaf(w, mlr.y, gl);
-                go.x = fmaf(w, v.x, go.x); go.y = fmaf(w, v.y, go.y); go.z = fmaf(w, v.z, go.z); go.w = fmaf(w, v.w, go.w);
+                if (it > 64) __nanosleep(100);
+                // once a wait of this process has run out, later ones give up early: a lost peer costs
+                // one limit, not one limit per row and layer
+                if (it == 4096 && (*(volatile unsigned int *)&g_status & TRB_ST_PEER_TIMEOUT)) break;
             }
-            if (!ok) raise_status(TRB_ST_PEER_TIMEOUT);
-            o = go; lsum = gl;
+            if (pending) {
+                raise_status(TRB_ST_PEER_TIMEOUT);
+            } else {
+                float gm = mmax;
+#pragma unroll
+                for (int r = 0; r < P2P_MAX_WORLD; ++r)
+                    if (r < p.p2p_world && r != p.p2p_rank) gm = fmaxf(gm, __uint_as_float(pk[r][2].x));
+                // weights and sums in rank order, own partial from registers
+                float gl = 0.f;
+                float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int r = 0; r < P2P_MAX_WORLD; ++r) {
+                    if (r >= p.p2p_world) continue;
+                    float2 mlr = make_float2(mmax, lsum);
+                    float4 v = o;
+                    if (r != p.p2p_rank) {
+                        v = make_float4(__uint_as_float(pk[r][0].x), __uint_as_float(pk[r][0].z), __uint_as_float(pk[r][1].x), __uint_as_float(pk[r][1].z));
+                        mlr = make_float2(__uint_as_float(pk[r][2].x), __uint_as_float(pk[r][2].z));
+                    }
+                    const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
+                    gl = fmaf(w, mlr.y, gl);
+                    go.x = fmaf(w, v.x, go.x); go.y = fmaf(w, v.y, go.y); go.z = fmaf(w, v.z, go.z); go.w = fmaf(w, v.w, go.w);
+                }
+                o = go; lsum = gl;
+            }
         }
         if (!lead) continue;
         const float inv = 1.f / lsum;
@@ -324,6 +358,7 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
         }
         *reinterpret_cast<uint2 *>(&p.out[grow * D + d4]) = *reinterpret_cast<const uint2 *>(ob);
     }
+    if (!all_ok) raise_status(TRB_ST_WAIT_TIMEOUT);
 }
 
 }  // namespace trb
@@ -348,6 +383,21 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 
     const int split = blockIdx.x, j = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- dependency plan: what may be touched before the wait was decided on the host -----
+    const int flags = p.pdl_flags;
+    bool waited = false;
+    // wait for the launches before this one (once per thread); unless the dependents were released
+    // at the top, they are released as soon as this launch's own dependencies are complete
+    auto dep_wait = [&]() {
+        if (!waited) {
+            pdl_wait();
+            waited = true;
+            if (!(flags & PDL_TRIGGER_TOP)) pdl_launch_dependents();
+        }
+    };
+    if (flags & PDL_TRIGGER_TOP) pdl_launch_dependents();
+    if (!(flags & PDL_PRE_CURSOR)) dep_wait();
 
     // ---- ranges, all derived from the device cursor -------------------------------------
     const long long pos = load_cursor(p.pos);
@@ -419,19 +469,34 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         }
     };
     const bool issuer = warp_on && nt_idx == 0 && grp_idx == 0;
-    // Rows written by the launch before this one (the append of this step) start at pos; tiles
-    // below them depend on nothing in flight, so their loads go out before the dependency wait and
-    // overlap the tail of the previous kernel in the stream.
-    const long long fresh_from = p.new_rows ? pos - p.shard_lo : (1LL << 62);
-    if (issuer)
-        for (int i = kw_idx; i < my_tiles && i < C::NSTAGE; i += p.kw)
-            if ((long long)(t0 + i + 1) * DEC_BN <= fresh_from) issue_tile(i);
-    pdl_wait();                       // predecessor complete: its rows, q, and the workspace are ours
-    pdl_launch_dependents();
-    const unsigned int epoch = threadIdx.x == 0 ? *(volatile unsigned int *)&p.counters[128 + j] : 0u;
-    if (issuer)
-        for (int i = kw_idx; i < my_tiles && i < C::NSTAGE; i += p.kw)
-            if ((long long)(t0 + i + 1) * DEC_BN > fresh_from) issue_tile(i);
+    // Rows that a launch still in flight may be writing (the append of this step) start at pos;
+    // tiles entirely below them are complete and stream at once, so that this launch overlaps the
+    // tail of the one before it.  The other tiles are requested only after the dependency wait,
+    // by their stream's issuer when it reaches them (they are the last tiles of the last split).
+    const long long fresh_from = (flags & PDL_ALL_STABLE) ? (1LL << 62) : (p.new_rows ? pos - p.shard_lo : 0);
+    int n_stable = my_tiles;                                   // tiles [0, n_stable) of this split are complete
+    if (!waited) {
+        long long ns = fresh_from / DEC_BN - t0;
+        if (ns < 0) ns = 0;
+        if (ns < n_stable) n_stable = (int)ns;
+    }
+    int next_issue = kw_idx;                                   // next tile of this warp's stream to request
+    bool pipe_ok = true;
+    auto issue_more = [&](int upto) {                          // request this stream's tiles below `upto`, in order
+        while (next_issue < upto && next_issue < my_tiles && (waited || next_issue < n_stable)) {
+            if (next_issue >= C::NSTAGE && !mbar_wait(&bar_empty[next_issue % C::NSTAGE], ((next_issue / C::NSTAGE) - 1) & 1)) {
+                pipe_ok = false;
+                break;
+            }
+            issue_tile(next_issue);
+            next_issue += p.kw;
+        }
+    };
+    if (issuer) issue_more(C::NSTAGE);
+    if (!(flags & PDL_PRE_Q)) {                                // the query rows may come from the launch before this one
+        dep_wait();
+        if (issuer) issue_more(C::NSTAGE);                     // ... and every row of the cache is complete now
+    }
 
     // ---- query fragments (the B operand of S^T = K Q^T) into shared memory, once per CTA:
     // warp w < nt prepares slice w; lane (g, t) owns column n = g (row 8w + g) and the dims
@@ -524,7 +589,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
 #pragma unroll 1
         for (int i = kw_idx; i < my_tiles; i += p.kw) {
             const int s = i % C::NSTAGE;
-            if (!mbar_wait(&bar_full[s], (i / C::NSTAGE) & 1)) break;
+            if (issuer && next_issue <= i) {                   // tile i was held back: its rows were still being written
+                dep_wait();
+                issue_more(i + C::NSTAGE);
+            }
+            if (!pipe_ok || !mbar_wait(&bar_full[s], (i / C::NSTAGE) & 1)) break;
             const int key0 = (t0 + i) * DEC_BN;                                    // virtual row of the tile
             if (key0 + gb < lloc_i && key0 + gb + 16 * GS - 1 >= row_lo_i) {
                 const uint32_t kt = smem_u32(smem + s * 2 * C::TILE);
@@ -683,9 +752,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_empty[s]);
-            if (issuer && i + C::NSTAGE < my_tiles) {          // refill the stage once every slice has left it
-                if (!mbar_wait(&bar_empty[s], (i / C::NSTAGE) & 1)) break;
-                issue_tile(i + C::NSTAGE);
+            if (issuer) {                                      // refill the stage once every slice has left it
+                issue_more(i + C::NSTAGE + 1);
+                if (!pipe_ok) break;
             }
         }
 #pragma unroll
@@ -697,57 +766,55 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
 
     // =============================== CTA epilogue =======================================
-    // 1. merge the kw warps that share an 8-row slice (fixed order), through shared memory
+    // Everything from here on touches the workspace and the outputs: the launches before this one
+    // must be complete.  One thread takes the kv head's ticket right away, so that its round trip
+    // runs under the merge below.
+    dep_wait();
+    unsigned long long ticket = 0ull;
+    if (threadIdx.x == 0) ticket = decode_ticket_take(p, j);
+    // 1. merge the warps that share an 8-row slice (fixed order) through shared memory: every warp
+    // stages its accumulators unscaled, together with its (max, sum); the reducing threads weigh them
     __syncthreads();                    // every stage has been consumed
     if (warp_on && g == 0) {
         sm_ml[(warp * 8 + 2 * t + 0) * 2 + 0] = mx[0]; sm_ml[(warp * 8 + 2 * t + 0) * 2 + 1] = ls[0];
         sm_ml[(warp * 8 + 2 * t + 1) * 2 + 0] = mx[1]; sm_ml[(warp * 8 + 2 * t + 1) * 2 + 1] = ls[1];
     }
-    __syncthreads();
     float *stage_acc = reinterpret_cast<float *>(smem);                // [warp][8][D + pad]
     constexpr int SROW = D + DEC_EPI_PAD;
     if (warp_on) {
-        float wgt[2];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            float mg = -INFINITY;
-            for (int k = 0; k < p.kw * GPT; ++k) mg = fmaxf(mg, sm_ml[((k * p.nt + nt_idx) * 8 + 2 * t + c) * 2]);
-            wgt[c] = mg == -INFINITY ? 0.f : fast_exp2(mx[c] - mg);
-        }
+        const bool live0 = 8 * nt_idx + 2 * t < p.rows, live1 = 8 * nt_idx + 2 * t + 1 < p.rows;
 #pragma unroll
         for (int a = 0; a < C::ACC; ++a)
 #pragma unroll
             for (int i = 0; i < 4; ++i)
-                stage_acc[(warp * 8 + 2 * t + (i & 1)) * SROW + acc_dim<FP8>(a, i, g)] = acc[a][i] * wgt[i & 1];
+                if ((i & 1) ? live1 : live0) stage_acc[(warp * 8 + 2 * t + (i & 1)) * SROW + acc_dim<FP8>(a, i, g)] = acc[a][i];
     }
-    __syncthreads();
+    if (threadIdx.x == 0) decode_ticket(p, j, active, DEC_CTHREADS / (D / 4), sm_flag, ticket);
+    __syncthreads();                    // also publishes the ticket's result (sm_flag)
     const int tid = threadIdx.x;                                       // 0..383 here
+    const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
     const long long part_base = ((long long)j * p.nsplit + split) * p.rows_pad;
+    const int nw = p.kw * GPT;                                         // warps per slice
     for (int item = tid; item < p.nt * 8 * (D / 4); item += DEC_CTHREADS) {
         const int row = item / (D / 4), d4 = (item % (D / 4)) * 4;
         if (row >= p.rows) continue;
         const int nti = row >> 3, qc = row & 7;
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int k = 0; k < p.kw * GPT; ++k) {
-            const float4 v = *reinterpret_cast<const float4 *>(&stage_acc[((k * p.nt + nti) * 8 + qc) * SROW + d4]);
-            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-        }
-        *reinterpret_cast<float4 *>(&p.part_acc[(part_base + row) * D + d4]) = sum;
-    }
-    for (int row = tid; row < p.rows; row += DEC_CTHREADS) {
-        const int nti = row >> 3, qc = row & 7;
         float mg = -INFINITY;
-        for (int k = 0; k < p.kw * GPT; ++k) mg = fmaxf(mg, sm_ml[((k * p.nt + nti) * 8 + qc) * 2]);
+        for (int k = 0; k < nw; ++k) mg = fmaxf(mg, sm_ml[((k * p.nt + nti) * 8 + qc) * 2]);
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
         float lg = 0.f;
-        for (int k = 0; k < p.kw * GPT; ++k) {
-            const float mk = sm_ml[((k * p.nt + nti) * 8 + qc) * 2], lk = sm_ml[((k * p.nt + nti) * 8 + qc) * 2 + 1];
-            lg += mk == -INFINITY ? 0.f : lk * fast_exp2(mk - mg);
+        for (int k = 0; k < nw; ++k) {
+            const float mk = sm_ml[((k * p.nt + nti) * 8 + qc) * 2];
+            const float w = mk == -INFINITY ? 0.f : fast_exp2(mk - mg);
+            const float4 v = *reinterpret_cast<const float4 *>(&stage_acc[((k * p.nt + nti) * 8 + qc) * SROW + d4]);
+            sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y); sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
+            lg = fmaf(w, sm_ml[((k * p.nt + nti) * 8 + qc) * 2 + 1], lg);
         }
-        p.part_ml[(part_base + row) * 2 + 0] = mg;
-        p.part_ml[(part_base + row) * 2 + 1] = lg;
+        st_tagged4(p.part_acc + (part_base + row) * D + d4, sum, tag);
+        if (d4 == 0) st_volatile_v4(p.part_ml + part_base + row, make_uint4(__float_as_uint(mg), tag, __float_as_uint(lg), tag));
     }
 
-    decode_tail<D, DEC_CTHREADS>(p, smem, sm_flag, j, active, epoch);
+    decode_tail<D, DEC_CTHREADS>(p, smem, sm_flag, j, active);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -851,8 +918,9 @@ static WorkspaceLayout workspace_layout(int hkv, int nsplit, int rows_pad, int d
     WorkspaceLayout w;
     w.counters = 0;
     w.ml = 1024;
-    w.acc = align_up(w.ml + (size_t)hkv * nsplit * rows_pad * 2 * sizeof(float), 256);
-    w.total = w.acc + (size_t)hkv * nsplit * rows_pad * d * sizeof(float);
+    // every float of a partial travels with a tag: (max, tag, sum, tag) and (value, tag) pairs
+    w.acc = align_up(w.ml + (size_t)hkv * nsplit * rows_pad * sizeof(uint4), 256);
+    w.total = w.acc + (size_t)hkv * nsplit * rows_pad * d * sizeof(uint2);
     return w;
 }
 
@@ -959,8 +1027,8 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     const WorkspaceLayout w = workspace_layout(c.hkv, p.nsplit, p.rows_pad, c.d);
     if (a->workspace_bytes < w.total) return TRB_E_CAPACITY;
     uint8_t *ws = (uint8_t *)a->workspace;
-    p.counters = (unsigned int *)(ws + w.counters);
-    p.part_ml = (float *)(ws + w.ml); p.part_acc = (float *)(ws + w.acc);
+    p.word = (unsigned long long *)(ws + w.counters);
+    p.part_ml = (uint4 *)(ws + w.ml); p.part_acc = (uint2 *)(ws + w.acc);
     p.shard_ml = a->partial_ml; p.shard_acc = a->partial_acc;
     p.p2p_world = 0; p.p2p_rank = 0;
     for (int r = 0; r < 8; ++r) p.p2p_ptr[r] = nullptr;
@@ -976,13 +1044,19 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     const int row_bytes = c.d * (c.fp8 ? 1 : 2);
     CUtensorMap mk, mv;
     cudaStream_t st = (cudaStream_t)stream;
-    if (c.fp8 && c.d == TC_D && c.ring == 0 && a->window == 0 && rows >= g_tc_min_rows) {
-        if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, row_bytes, TC_BN, &mk))) return rc;
-        if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, row_bytes, TC_BN, &mv))) return rc;
-        return launch_decode_tc(mk, mv, p, st);
-    }
-    if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, row_bytes, DEC_BN, &mk))) return rc;
-    if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, row_bytes, DEC_BN, &mv))) return rc;
+    const bool tensor_kernel = c.fp8 && c.d == TC_D && c.ring == 0 && a->window == 0 && rows >= g_tc_min_rows;
+    if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, row_bytes, tensor_kernel ? TC_BN : DEC_BN, &mk))) return rc;
+    if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, row_bytes, tensor_kernel ? TC_BN : DEC_BN, &mv))) return rc;
+    // nothing fails after this point except the launch itself: record the launch for the next one
+    const size_t out_rows = (size_t)a->m * a->hq;
+    const WrittenRange outs[3] = {{a->out, a->out ? out_rows * c.d * sizeof(__nv_bfloat16) : 0},
+                                  {a->partial_ml, a->partial_ml ? out_rows * 2 * sizeof(float) : 0},
+                                  {a->partial_acc, a->partial_acc ? out_rows * c.d * sizeof(float) : 0}};
+    p.pdl_flags = pdl_plan_decode(st, c.k, &a->pos, p.new_rows, WrittenRange{a->q, out_rows * c.d * sizeof(__nv_bfloat16)}, outs);
+    // a ring cache maps several positions to one row: the rows below the cursor are not the rows
+    // below the in-flight append
+    if (c.ring > 0 && !(p.pdl_flags & PDL_ALL_STABLE)) p.pdl_flags &= PDL_TRIGGER_TOP;
+    if (tensor_kernel) return launch_decode_tc(mk, mv, p, st);
     if (c.d == 256) return c.fp8 ? launch_decode<256, true>(mk, mv, p, st) : launch_decode<256, false>(mk, mv, p, st);
     return c.fp8 ? launch_decode<128, true>(mk, mv, p, st) : launch_decode<128, false>(mk, mv, p, st);
 }
@@ -993,6 +1067,7 @@ extern "C" int trb_attn_block_partial(const void *q, const void *k_blk, const vo
     if (d != 128 && d != 256) return TRB_E_UNSUPPORTED;
     const float sl2 = scale * 1.4426950408889634f;
     cudaStream_t st = (cudaStream_t)stream;
+    pdl_note_fence((cudaStream_t)stream);
     if (d == 256)
         block_partial_kernel<256><<<b * hq, 32, 0, st>>>((const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_blk,
                                                          (const __nv_bfloat16 *)v_blk, b, hq, hkv, sl2, extra_ml, extra_acc);
@@ -1008,6 +1083,7 @@ extern "C" int trb_lse_merge(const float *ml, const float *acc, int32_t n_parts,
                              trb_stream_t stream) {
     if (!ml || !acc || !out || n_parts < 1 || rows < 1 || d < 4 || (d % 4) || hq < 1) return TRB_E_ARG;
     if (((uintptr_t)acc & 15) || ((uintptr_t)out & 7)) return TRB_E_ALIGN;
+    pdl_note_fence((cudaStream_t)stream);
     lse_merge_kernel<<<rows, 64, 0, (cudaStream_t)stream>>>(ml, acc, n_parts, rows, d, (__nv_bfloat16 *)out,
                                                              (const __nv_bfloat16 *)gate, gate_row_stride, gate_head_stride, hq);
     TRB_CUDA_CHECK(cudaGetLastError());
@@ -1047,18 +1123,33 @@ static int static_scratch_ptr(void **out) {
 }
 }  // namespace trb
 
+namespace trb {
+// count <- 0 and epoch <- epoch + 1 in every ticket word: a call that was cut short leaves
+// neither a count nor tagged partials that a later call could take for its own
+__global__ void static_scratch_reset_kernel(unsigned long long *word, int n) {
+    const int i = threadIdx.x;
+    if (i < n) word[i] = ((word[i] >> 16) + 1ull) << 16;
+}
+}  // namespace trb
+
 extern "C" int trb_attn_decode_static(const trb_cache_t *cache, const trb_decode_args_t *args, trb_stream_t stream) {
     if (!cache || !args) return TRB_E_ARG;
-    if (cache->hkv < 1 || args->hq < 1 || args->m < 1 || args->hq % cache->hkv) return TRB_E_ARG;
+    if (cache->hkv < 1 || cache->hkv > 64 || args->hq < 1 || args->m < 1 || args->hq % cache->hkv) return TRB_E_ARG;
+    // The exchange between GPUs is tagged with the launch count of the workspace, which must be the
+    // same on every GPU; the built-in array is shared by all callers of a process, so its count is not.
+    if (args->p2p_xchg) return TRB_E_UNSUPPORTED;
     const size_t need = trb_decode_workspace_bytes(args->hq, cache->hkv, cache->d, args->m);
     if (need == 0) return TRB_E_UNSUPPORTED;
     if (need > TRB_STATIC_SCRATCH_BYTES) return TRB_E_SCRATCH_LIMIT;
     void *scratch = nullptr;
     int rc = static_scratch_ptr(&scratch);
     if (rc) return rc;
-    // The array keeps whatever the previous call left.  Only the header (tickets, claims, epochs)
-    // has to start from zero; the partials are fully rewritten before they are read.
-    TRB_CUDA_CHECK(cudaMemsetAsync(scratch, 0, 1024, (cudaStream_t)stream));
+    // The array keeps whatever the previous call left.  Only the arrival counts in the header have
+    // to start from zero; the partials are recognised by their tags, so nothing else is cleared.
+    cudaStream_t st = (cudaStream_t)stream;
+    pdl_note_fence(st);
+    static_scratch_reset_kernel<<<1, 64, 0, st>>>((unsigned long long *)scratch, cache->hkv);
+    TRB_CUDA_CHECK(cudaGetLastError());
     trb_decode_args_t a = *args;
     a.workspace = scratch;
     a.workspace_bytes = TRB_STATIC_SCRATCH_BYTES;

@@ -83,6 +83,19 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const int split = blockIdx.x, j = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
 
+    // ---- dependency plan (see decode_kernel) ----
+    const int flags = p.pdl_flags;
+    bool waited = false;
+    auto dep_wait = [&]() {
+        if (!waited) {
+            pdl_wait();
+            waited = true;
+            if (!(flags & PDL_TRIGGER_TOP)) pdl_launch_dependents();
+        }
+    };
+    if (flags & PDL_TRIGGER_TOP) pdl_launch_dependents();
+    if (!(flags & PDL_PRE_CURSOR)) dep_wait();
+
     // ---- ranges, all derived from the device cursor (as in decode_kernel, in 128-key tiles) ----
     const long long pos = load_cursor(p.pos);
     const long long live = pos + (p.new_rows ? p.m : 0);
@@ -147,15 +160,19 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             tma_load_4d(vt + TC_BN * 128, &tm_v, &v_full[s], 0, 1, row0, j);
         }
     };
-    // Tiles below the rows that the preceding append writes depend on nothing in flight: the first
-    // two of them are requested before the dependency wait.
-    const long long fresh_from = p.new_rows ? pos - p.shard_lo : (1LL << 62);
+    // Tiles below the rows that a launch still in flight may be writing are complete: they stream
+    // before the dependency wait (the producer warp waits when it reaches the first other tile).
+    const long long fresh_from = (flags & PDL_ALL_STABLE) ? (1LL << 62) : (p.new_rows ? pos - p.shard_lo : 0);
+    int n_stable = my_tiles;
+    if (!waited) {
+        long long ns = fresh_from / TC_BN - t0;
+        if (ns < 0) ns = 0;
+        if (ns < n_stable) n_stable = (int)ns;
+    }
     int pre = 0;
     if (warp == W_TMA)
-        while (pre < my_tiles && pre < 2 && (long long)(t0 + pre + 1) * TC_BN <= fresh_from) { issue_k(pre); issue_v(pre); ++pre; }
-    pdl_wait();
-    pdl_launch_dependents();
-    const unsigned int epoch = tid == 0 ? *(volatile unsigned int *)&p.counters[128 + j] : 0u;
+        while (pre < my_tiles && pre < 2 && pre < n_stable) { issue_k(pre); issue_v(pre); ++pre; }
+    if (!(flags & PDL_PRE_Q)) dep_wait();                      // the query rows may come from the launch before this one
 
     // ---- query block: rows r of this kv head (query r / g, head j g + r % g) as two stacked e4m3
     // copies with a power-of-two row scale; thread = (row, 32-dim eighth).  (The bytes of a
@@ -215,11 +232,16 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if (warp == W_TMA) {
         // ================================ TMA producer ================================
         for (int i = pre; i < my_tiles; ++i) {
+            if (i >= n_stable) dep_wait();                     // rows that were still being written when this launch began
             if (i >= TC_KSLOTS && !mbar_wait(&k_free[i % TC_KSLOTS], ((i / TC_KSLOTS) & 1) ^ 1)) break;
             issue_k(i);
             if (i >= TC_VSLOTS && !mbar_wait(&v_free[i % TC_VSLOTS], ((i / TC_VSLOTS) & 1) ^ 1)) break;
             issue_v(i);
         }
+        // this warp is idle from here on: it takes the kv head's ticket (workspace: after the wait)
+        dep_wait();
+        if (lane == 0) decode_ticket(p, j, active, NTHREADS / (D / 4), sm_flag, decode_ticket_take(p, j));
+        named_barrier(15, NTHREADS);
     } else if (warp == W_MMA) {
         // ================================ MMA issuer ==================================
         // order on the tensor pipe: QK(0), QK(1), PV(0), QK(2), PV(1), ...
@@ -268,6 +290,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             }
             __syncwarp();
         }
+        named_barrier(15, NTHREADS);
     } else if (warp < 4 * NCH) {
         // ====== softmax / correction / epilogue: one warpgroup per 16 query rows; thread = key lane = dim lane ======
         const int rg = warp >> 2, qw = warp & 3;                               // row group, lane quarter
@@ -292,18 +315,28 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         uint32_t unset = 0xffffu;
         float *g_wmax = sm_wmax + rg * 64;                                     // [4 quarters][16 rows], slow path only
 
-        for (int i = 0; i < my_tiles && ok; ++i) {
+        // A warp whose bounded wait ran out is `dead`: it stops waiting and computing, but still takes
+        // part in its group's named barriers, which the three sibling warps keep reaching.
+        bool dead = false;
+        for (int i = 0; i < my_tiles; ++i) {
             const int s = i % TC_KSLOTS, b = i & 1;
             const int kv = (t0 + i) * TC_BN + kl;                              // virtual row of this thread's key
-            if (!(ok = mbar_wait(&k_full[s], (i / TC_KSLOTS) & 1))) break;
-            const float ksc = sm_sc[(s * 2 + 0) * TC_BN + kl], vsc = sm_sc[(s * 2 + 1) * TC_BN + kl];
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&k_free[s]);                            // the scale slot may be refilled
+            if (!dead && !mbar_wait(&k_full[s], (i / TC_KSLOTS) & 1)) dead = true;
+            float ksc = 0.f, vsc = 0.f;
+            if (!dead) {
+                ksc = sm_sc[(s * 2 + 0) * TC_BN + kl]; vsc = sm_sc[(s * 2 + 1) * TC_BN + kl];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&k_free[s]);                        // the scale slot may be refilled
+            }
             const bool key_ok = kv < lloc_i && vsc > 0.f;
             const float kfac = ksc * p.scale_log2;
             const float vlog = key_ok ? __log2f(vsc) : 0.f;
             const float vinv = key_ok ? __fdividef(0.0078125f, vsc) : 0.f;      // 1 / (128 v_scale)
-            if (!(ok = mbar_wait(&s_full[b], (i >> 1) & 1))) break;
+            if (!dead && !mbar_wait(&s_full[b], (i >> 1) & 1)) dead = true;
+            if (dead) {
+                if (barrier_or(bar_id, 128, false)) named_barrier(bar_id, 128);
+                continue;
+            }
             tc_fence_after();
             float tv[16];
             {
@@ -368,7 +401,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 unset &= ~upd;
                 if (i > 0) {
                     // correct the O^T columns of the updated rows; PV(i-1) must have landed
-                    if (!(ok = mbar_wait(&pv_done[b ^ 1], ((i - 1) >> 1) & 1))) break;
+                    if (!mbar_wait(&pv_done[b ^ 1], ((i - 1) >> 1) & 1)) { dead = true; continue; }
                     tc_fence_after();
 #pragma unroll 1
                     for (uint32_t mk = upd; mk; mk &= mk - 1) {
@@ -383,7 +416,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 }
             }
             // the P buffer of tile i-2 must have been consumed
-            if (i >= 2 && !(ok = mbar_wait(&pv_done[b], ((i >> 1) & 1) ^ 1))) break;
+            if (i >= 2 && !mbar_wait(&pv_done[b], ((i >> 1) & 1) ^ 1)) { dead = true; continue; }
             // ---- probabilities 2^(t - ref + 7) as hi + lo e4m3 codes: this key's 16 rows are 16 + 16 bytes
             uint32_t hw[4], lw[4];
 #pragma unroll
@@ -409,8 +442,12 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             if (lane == 0) mbar_arrive(&p_full[b]);
         }
         // ---- epilogue: this CTA's partial rows.  acc[row][dim] = (hi + lo part of O^T[dim][row]) / 128
+        ok = !dead;
         if (ok && my_tiles > 0) ok = mbar_wait(&pv_done[(my_tiles - 1) & 1], ((my_tiles - 1) >> 1) & 1);
         tc_fence_after();
+        dep_wait();                                                            // the workspace belongs to this launch now
+        named_barrier(15, NTHREADS);                                           // the ticket (taken by the producer warp) is in sm_flag
+        const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
         const long long part_base = ((long long)j * p.nsplit + split) * p.rows_pad;
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
@@ -426,7 +463,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
                 const int r = r0 + e;
-                if (r < p.rows) p.part_acc[(part_base + r) * D + h * 128 + kl] = (hi[e] + lo[e]) * 0.0078125f;
+                if (r < p.rows) p.part_acc[(part_base + r) * D + h * 128 + kl] = make_uint2(__float_as_uint((hi[e] + lo[e]) * 0.0078125f), tag);
             }
         }
         tc_fence_before();
@@ -473,12 +510,14 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             float cr = 0.f;                                                    // cref[kl] without dynamic register indexing
 #pragma unroll
             for (int r = 0; r < 16; ++r) cr = kl == r ? cref[r] : cr;
-            *reinterpret_cast<float2 *>(&p.part_ml[(part_base + r0 + kl) * 2]) = make_float2(((unset >> kl) & 1u) ? -INFINITY : 7.f - cr, l);
+            st_volatile_v4(p.part_ml + part_base + r0 + kl,
+                           make_uint4(__float_as_uint(((unset >> kl) & 1u) ? -INFINITY : 7.f - cr), tag, __float_as_uint(l), tag));
         }
     }
+    dep_wait();
     __syncthreads();
     if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TC_TMEM_COLS); }
-    decode_tail<D, NTHREADS>(p, smem, sm_flag, j, active, epoch);
+    decode_tail<D, NTHREADS>(p, smem, sm_flag, j, active);
 }
 
 }  // namespace trb

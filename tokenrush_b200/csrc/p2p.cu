@@ -203,6 +203,7 @@ extern "C" int trb_p2p_merge(const trb_p2p_merge_args_t *a, trb_stream_t stream)
     p.seq = a->seq; p.ml = a->partial_ml; p.acc = a->partial_acc;
     p.out = (__nv_bfloat16 *)a->out; p.gate = (const __nv_bfloat16 *)a->gate;
     p.gate_rs = a->gate_row_stride; p.gate_hs = a->gate_head_stride;
+    pdl_note_fence((cudaStream_t)stream);
     p2p_merge_kernel<<<a->rows, a->d / 4, 0, (cudaStream_t)stream>>>(p);
     TRB_CUDA_CHECK(cudaGetLastError());
     return TRB_OK;

@@ -373,6 +373,7 @@ extern "C" int trb_attn_prefill(const trb_cache_t *cache, const void *q, void *o
         attr_set[dev & 63] = true;
     }
     dim3 grid((t + PF_BM - 1) / PF_BM, hq);
+    pdl_note_fence((cudaStream_t)stream);
     prefill_kernel<<<grid, PF_THREADS, PF_SMEM, (cudaStream_t)stream>>>(mk, mv, p);
     TRB_CUDA_CHECK(cudaGetLastError());
     return TRB_OK;

@@ -5,6 +5,7 @@
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 #include "common.cuh"
 #include "tmap.h"
@@ -15,19 +16,132 @@ void trb_set_last_cuda_error(cudaError_t e, const char *file, int line) {
     snprintf(g_last_cuda, sizeof(g_last_cuda), "%s (%s:%d)", cudaGetErrorString(e), file, line);
 }
 
+// ------------------------------------------------------------------ programmatic launch plans
 static int g_pdl = -1;
+
 namespace trb {
-bool pdl_enabled() {
+
+int pdl_mode() {
     if (g_pdl < 0) {
         const char *e = getenv("TRB_PDL");
-        g_pdl = (e && e[0] == '0') ? 0 : 1;
+        g_pdl = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
     }
-    return g_pdl != 0;
+    return g_pdl;
 }
+
+namespace {
+struct InFlight {
+    const void *cache_k;          // cache whose rows this launch writes (nullptr: none)
+    const void *cur_dev;          // ... at this cursor
+    long long cur_host;
+    WrittenRange w[3];            // other memory it writes (q_out of attn_prep, outputs of a decode)
+};
+struct StreamTrack {
+    std::vector<InFlight> s;      // library launches that may still be running when the next one starts
+    unsigned long long capture_id = 0;
+    int capture_status = 0;
+};
+std::mutex g_track_mu;
+std::unordered_map<cudaStream_t, StreamTrack> g_track;
+constexpr size_t MAX_IN_FLIGHT = 64;
+
+// The list belongs to one stretch of stream order: a stream that enters or leaves graph capture
+// (or starts another capture) starts an empty list, because what precedes a captured node at
+// replay time is not what preceded the call at capture time.
+StreamTrack &track_of(cudaStream_t st) {
+    StreamTrack &t = g_track[st];
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    unsigned long long id = 0;
+    if (cudaStreamGetCaptureInfo(st, &status, &id) != cudaSuccess) {
+        (void)cudaGetLastError();
+        status = cudaStreamCaptureStatusNone;
+        id = 0;
+        t.s.clear();
+    }
+    if ((int)status != t.capture_status || id != t.capture_id) {
+        t.s.clear();
+        t.capture_status = (int)status;
+        t.capture_id = id;
+    }
+    return t;
+}
+bool overlaps(const WrittenRange &a, const WrittenRange &b) {
+    if (!a.lo || !b.lo || !a.bytes || !b.bytes) return false;
+    const uintptr_t a0 = (uintptr_t)a.lo, b0 = (uintptr_t)b.lo;
+    return a0 < b0 + b.bytes && b0 < a0 + a.bytes;
+}
+}  // namespace
+
+int pdl_plan_writer(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, WrittenRange extra) {
+    const int mode = pdl_mode();
+    if (mode == 0) return PDL_WAIT_FIRST;
+    std::lock_guard<std::mutex> lock(g_track_mu);
+    StreamTrack &t = track_of(st);
+    InFlight me = {cache_k, pos ? pos->dev : nullptr, pos ? pos->host : 0, {extra, {nullptr, 0}, {nullptr, 0}}};
+    // Triggering before the wait is harmless for this kernel (it reads its inputs after its wait);
+    // whoever starts because of it decides from the list what it may touch.  The first launch
+    // of a chain waits first, so that everything before the chain is complete for all of it.
+    const bool chained = mode == 2 && !t.s.empty() && t.s.size() < MAX_IN_FLIGHT;
+    if (!chained) t.s.clear();
+    t.s.push_back(me);
+    return chained ? PDL_TRIGGER_TOP : PDL_WAIT_FIRST;
+}
+
+int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, int new_rows, WrittenRange q,
+                    const WrittenRange (&out)[3]) {
+    const int mode = pdl_mode();
+    if (mode == 0) return 0;
+    std::lock_guard<std::mutex> lock(g_track_mu);
+    StreamTrack &t = track_of(st);
+    int flags = 0;
+    // With an empty list nothing is known about what precedes this launch: it waits at its top
+    // and becomes the point before which everything is complete.
+    if (!t.s.empty() && t.s.size() < MAX_IN_FLIGHT) {
+        int writers = 0;
+        bool same_rows = true, q_clean = true;
+        for (const InFlight &e : t.s) {
+            if (e.cache_k && e.cache_k == cache_k) {
+                ++writers;
+                // the rows in flight must be the ones this decode expects at its cursor
+                if (!new_rows || e.cur_dev != pos->dev || e.cur_host != pos->host) same_rows = false;
+            }
+            for (const WrittenRange &w : e.w)
+                if (overlaps(w, q)) q_clean = false;
+        }
+        if (writers == 0 || same_rows) {
+            flags |= PDL_PRE_CURSOR;
+            if (writers == 0) flags |= PDL_ALL_STABLE;
+            if (q_clean) flags |= PDL_PRE_Q;
+            if (mode == 2) flags |= PDL_TRIGGER_TOP;
+        }
+    }
+    InFlight me = {nullptr, nullptr, 0, {out[0], out[1], out[2]}};
+    if (!(flags & PDL_TRIGGER_TOP)) t.s.clear();      // it triggers after its wait: only it is in flight afterwards
+    t.s.push_back(me);
+    return flags;
+}
+
+void pdl_note_fence(cudaStream_t st) {
+    std::lock_guard<std::mutex> lock(g_track_mu);
+    auto it = g_track.find(st);
+    if (it != g_track.end()) it->second.s.clear();
+}
+
 }  // namespace trb
 
-extern "C" int trb_set_programmatic_launch(int enable) {
-    g_pdl = enable ? 1 : 0;
+extern "C" int trb_set_programmatic_launch(int mode) {
+    if (mode < 0 || mode > 2) return TRB_E_ARG;
+    std::lock_guard<std::mutex> lock(trb::g_track_mu);
+    g_pdl = mode;
+    trb::g_track.clear();
+    return TRB_OK;
+}
+
+extern "C" int trb_set_wait_limits(uint32_t pipeline_polls, uint32_t tail_polls, uint32_t peer_polls) {
+    const unsigned int v[3] = {pipeline_polls ? pipeline_polls : 1u << 20, tail_polls ? tail_polls : 1u << 17,
+                               peer_polls ? peer_polls : 1u << 22};
+    TRB_CUDA_CHECK(cudaDeviceSynchronize());
+    TRB_CUDA_CHECK(cudaMemcpyToSymbol(trb::c_wait_limit, v, sizeof(v)));
     return TRB_OK;
 }
 
@@ -44,7 +158,7 @@ extern "C" const char *trb_strerror(int code) {
         case TRB_E_DEVICE: return "device status word is non-zero";
         case TRB_E_SCRATCH_LIMIT:
             return "trb_attn_decode_static: this geometry needs more split scratch than the built-in "
-                   "TRB_STATIC_SCRATCH_BYTES (4 MiB); call trb_attn_decode with a caller-provided workspace";
+                   "TRB_STATIC_SCRATCH_BYTES (8 MiB); call trb_attn_decode with a caller-provided workspace";
         default: return "unknown error";
     }
 }

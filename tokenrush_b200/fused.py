@@ -66,12 +66,25 @@ def _cache(k_cache, v_cache, k_scale, v_scale, ring: int = 0, shard_lo=None) -> 
                    0 if shard_lo is None else 1, max_len, ring, 0 if shard_lo is None else int(shard_lo))
 
 
+def set_launch_mode(mode: int):
+    """0: ordinary launches; 1 (default): programmatic dependent launch, every kernel waits before
+    it releases the next one; 2: chained - a decode step made of calls of this module only (as in a
+    captured graph) overlaps each layer's scan with the tail of the layer before it.  In mode 2 the
+    caller promises that nothing else writes the caches, cursors or query rows between two calls
+    of this module on one stream.  See trb_set_programmatic_launch in include/trb_kv.h."""
+    L.check(L.lib().trb_set_programmatic_launch(int(mode)), "trb_set_programmatic_launch")
+
+
 def _workspace(device, hq: int, hkv: int, d: int) -> torch.Tensor:
-    """Split-partial scratch + tickets, one per (device, stream, geometry), zeroed once.
+    """Split-partial scratch + ticket words, one per (device, stream, geometry), zeroed once.
     Calls that share it are ordered by the stream."""
     key = (device.index, _stream(), hq, hkv, d)
     ws = _workspaces.get(key)
     if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            # a zero-fill recorded into the graph would wipe the launch count at every replay
+            raise RuntimeError("the first decode call of a (device, stream, geometry) allocates and zeroes its workspace: "
+                               "make it outside graph capture (run the step once on the capture stream first)")
         g = hq // hkv
         n = L.lib().trb_decode_workspace_bytes(hq, hkv, d, max(1, 48 // g))
         if n == 0:
