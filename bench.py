@@ -22,6 +22,8 @@ Workloads (synthetic: N(0,1) values quantised into the FP8 cache layout, seeded)
                  the FP8 cache in the same step)
     profile-decode / profile-prefill
                  small, self-ending cases of one kernel for a profiler (--rows, --m, --t)
+    timeline     per-phase time stamps of the M = 1 decode kernel's CTAs (needs the diagnostic
+                 library: python -m tokenrush_b200.build --timeline), --rows live rows, 16 layers
 Inputs are far larger than L2 (126 MB), so consecutive steps cannot be served from cache.
 
 The default single-GPU run reports window256k as the headline and attaches short runs of ctx32k,
@@ -61,6 +63,7 @@ WORKLOADS = {
     "prefill8k": dict(ctx=131072, t=8192),
     "profile-decode": dict(profile="decode"),
     "profile-prefill": dict(profile="prefill"),
+    "timeline": dict(profile="timeline"),
 }
 # DRAM bytes moved per live row by one launch of the decode kernels (dram__bytes_read.sum +
 # dram__bytes_write.sum of one ncu capture divided by the rows of that launch; the traffic is
@@ -608,6 +611,103 @@ def run_profile_case(args):
     print(json.dumps({"profile_case": kind, "rows": rows, "device_status": tb._lib.device_status()}), flush=True)
 
 
+TL_NAMES = ["cta start", "ranges known, barriers set", "first tiles requested", "query staged", "first tile landed", "last tile consumed",
+            "dependency wait passed", "all warps in the epilogue", "partial on its way", "tail: start", "tail: (max, sum) of all splits here",
+            "tail: accumulators merged", "cta leaves"]
+
+
+def run_timeline(args):
+    """Where the time of a decode launch goes: thread 0 of every CTA stamps %globaltimer at fixed points
+    (diagnostic build of the library); this prints, for the last launches of a captured step, every
+    stamp relative to the first CTA start of its launch, and how launches overlap."""
+    import ctypes as C
+    import numpy as np
+    import tokenrush_b200 as tb
+    lib = tb._lib.lib()
+    if not hasattr(lib, "trb_dbg_timeline"):
+        raise SystemExit("the loaded library has no timeline: build it with `python -m tokenrush_b200.build --timeline`")
+    lib.trb_dbg_timeline.argtypes, lib.trb_dbg_timeline.restype = [C.c_void_p, C.c_size_t], C.c_int
+    rows, m = args.rows or 32768, 1
+    tb.fused.set_launch_mode(args.launch_mode)
+    cfg = tb.AttnConfig(n_attn=LAYERS)
+    st = tb.State(cfg, rows + 256, "cuda", kv_dtype=torch.float8_e4m3fn)
+    random_fill_(st)
+    st.set_pos(rows - m)
+    q = torch.randn(LAYERS, m, HQ * D, device="cuda").to(torch.bfloat16)
+    kn = torch.randn(LAYERS, HKV, m, D, device="cuda").to(torch.bfloat16)
+    out = torch.zeros(LAYERS, m, HQ * D, device="cuda", dtype=torch.bfloat16)
+
+    def step():
+        for l in range(LAYERS):
+            if not args.decode_only:
+                tb.fused.kv_write_prefill(kn[l], kn[l], st, l, st.pos_t)
+            tb.fused.attn_decode_fused(q[l], None, st.k[l], st.v[l], st.pos_t, cfg, st.k_scale[l], st.v_scale[l], out=out[l])
+        if not args.decode_only:
+            tb.fused.cursor_advance(st.pos_t, m)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        step()
+    for _ in range(5):
+        g.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(3):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us_step = e0.elapsed_time(e1) * 1e3 / 3
+    buf = np.zeros((64, 256, 16), dtype=np.uint64)
+    assert lib.trb_dbg_timeline(buf.ctypes.data, buf.nbytes) == 0
+    t = buf.astype(np.int64)
+    # the 16 launches of the last replay: the 16 ring slots with the latest start stamps
+    starts = np.where(t[:, :, 0] > 0, t[:, :, 0], 0).max(axis=1)
+    order = [int(i) for i in np.argsort(starts) if starts[i] > 0][-LAYERS:]
+    launches = []
+    prev_end = None
+    for slot in order:
+        a = t[slot]
+        valid = (a[:, 0] > starts[slot] - 2_000_000) & (a[:, 12] > 0)
+        a = a[valid]
+        t0 = a[:, 0].min()
+        rec = {"ctas": int(valid.sum()), "first_start_to_last_leave_us": round((a[:, 12].max() - t0) / 1e3, 2),
+               "cta_start_spread_us": round((a[:, 0].max() - t0) / 1e3, 2)}
+        if prev_end is not None:
+            rec["first_start_minus_previous_launch_end_us"] = round((t0 - prev_end) / 1e3, 2)
+        prev_end = a[:, 12].max()
+        helpers = a[:, 13].astype(np.int32) >= 0
+        phases = {}
+        for i, nm in enumerate(TL_NAMES):
+            col = a[:, i]
+            sel = col > 0
+            if i in (9, 10, 11):
+                sel &= helpers
+            if sel.any():
+                c = (col[sel] - t0) / 1e3
+                phases[nm] = [round(float(c.min()), 2), round(float(np.median(c)), 2), round(float(c.max()), 2)]
+        rec["stamps_us_min_median_max"] = phases
+        # per CTA: time between consecutive stamps (median over CTAs)
+        seg = {}
+        for (i, j2, nm) in ((0, 4, "start -> first tile landed"), (4, 5, "streaming"), (5, 7, "last tile -> all warps done"),
+                            (7, 8, "CTA merge + partial store"), (8, 12, "helpers: partial -> leave")):
+            sel = (a[:, i] > 0) & (a[:, j2] > 0)
+            if nm.startswith("helpers"):
+                sel &= helpers
+            if sel.any():
+                seg[nm] = round(float(np.median((a[sel, j2] - a[sel, i]) / 1e3)), 2)
+        rec["per_cta_median_us"] = seg
+        launches.append(rec)
+    print(json.dumps({"timeline": {"rows": rows, "layers": LAYERS, "launch_mode": args.launch_mode, "decode_only": bool(args.decode_only),
+                                   "us_per_step": round(us_step, 2), "us_per_layer": round(us_step / LAYERS, 2), "stamp_names": TL_NAMES,
+                                   "launches": launches[-4:], "device_status": tb._lib.device_status()}}), flush=True)
+
+
 def summary_of(line):
     """The part of a workload's line that the headline line carries under `workloads`."""
     keys = ("metric", "value", "unit", "us_per_step", "ms_per_step", "steps", "warmup", "blocks", "e2e", "clocks", "gpu_launches", "device_status")
@@ -879,8 +979,12 @@ def main():
     ap.add_argument("--t", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--decode-only", action="store_true", help="timeline: a graph of the 16 decode launches without appends")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "timeline":
+        os.environ["TRB_KV_LIB"] = os.path.join(ROOT, "tokenrush_b200", "libtrb_kv_timeline.so")   # read when the package is imported
+        run_timeline(args)
+    elif args.impl == "reference":
         run_reference(args)
     elif "profile" in WORKLOADS[args.workload]:
         run_profile_case(args)

@@ -81,9 +81,10 @@ def test_tail_wait_runs_out_on_a_stale_ticket_and_reports(tb):
     tb.fused.attn_decode_fused(q, None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0], st.v_scale[0])
     torch.cuda.synchronize()
     assert tb._lib.device_status() == 0
-    ws = tb.fused._workspace(q.device, HQ, HKV, D)
-    words = ws[:64 * 8].view(torch.int64)
-    words[0] += active - 1
+    ws = tb.fused.workspace_tensor(q.device, HQ, HKV, D, 1)
+    slot_bytes = ws.numel() // tb.fused.WORKSPACE_SLOTS
+    for s_ in range(tb.fused.WORKSPACE_SLOTS):                   # whichever slot the next call gets
+        ws[s_ * slot_bytes:s_ * slot_bytes + 8].view(torch.int64)[0] += active - 1
     assert lib.trb_set_wait_limits(0, 2000, 0) == 0
     tb.fused.attn_decode_fused(q, None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0], st.v_scale[0])
     torch.cuda.synchronize()                                     # the launch returned
@@ -100,8 +101,10 @@ def test_unzeroed_workspace_is_reported(tb):
     q = to_dev(O.seeded_bf16(3, 1, HQ, D)).reshape(1, -1)
     tb.fused.attn_decode_fused(q, None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0], st.v_scale[0])
     torch.cuda.synchronize()
-    ws = tb.fused._workspace(q.device, HQ, HKV, D)
-    ws[:64 * 8].view(torch.int64)[1] = 1000                      # an arrival count no launch can produce
+    ws = tb.fused.workspace_tensor(q.device, HQ, HKV, D, 1)
+    slot_bytes = ws.numel() // tb.fused.WORKSPACE_SLOTS
+    for s_ in range(tb.fused.WORKSPACE_SLOTS):                   # whichever slot the next call gets
+        ws[s_ * slot_bytes + 8:s_ * slot_bytes + 16].view(torch.int64)[0] = 1000   # kv head 1: an arrival count no launch can produce
     tb.fused.attn_decode_fused(q, None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0], st.v_scale[0])
     torch.cuda.synchronize()
     assert tb._lib.device_status() & Lb.ST_WORKSPACE

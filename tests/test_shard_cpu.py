@@ -94,3 +94,69 @@ def test_shard_partition_helpers():
     for live in (0, 1, 512, 513, 2048, 2060):
         rows = [shard.live_rows(r, 4, 2048, live, headroom=32) for r in range(4)]
         assert sum(rows) == min(live, 2048 + 32) and all(0 <= x for x in rows)
+
+
+def test_resume_plan_and_ring_validity():
+    # owner of the resume position and live rows after a rewind across shard boundaries
+    plan = shard.resume_plan(1300, 4, 2048, headroom=32)
+    assert plan["owner"] == 2 and plan["live"] == [512, 512, 276, 0]
+    assert shard.resume_rows_dropped(2060, 1300, 4, 2048, headroom=32) == [0, 0, 236, 524]
+    assert shard.resume_plan(0, 4, 2048)["live"] == [0, 0, 0, 0] and shard.resume_plan(0, 4, 2048)["owner"] == 0
+    assert shard.resume_plan(2048, 4, 2048, headroom=8)["owner"] == 3          # past the window: the last rank's headroom
+    with pytest.raises(ValueError):
+        shard.resume_plan(2100, 4, 2048, headroom=8)
+    # the reference's draft geometry: ring 4096 = smallest power of two >= 2048 + 8 + 8, slack 2032
+    ring = O.ring_size(2048, 8)
+    assert ring == 4096
+    assert shard.ring_snapshot_valid(1000, 1000 + 2032, ring, 2048, 8)
+    assert not shard.ring_snapshot_valid(1000, 1000 + 2033, ring, 2048, 8)
+
+
+def _resume_worker(rank, world, port, window, L, P, out_q):
+    """Fill to L, decode; rewind to P (across shard boundaries), append other rows, decode again: the
+    merged result must equal an unsharded sequence that was rewound the same way."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        kb, vb = O.seeded_bf16(1, HKV, L, D), O.seeded_bf16(2, HKV, L, D)
+        k2, v2 = O.seeded_bf16(4, HKV, 1, D), O.seeded_bf16(5, HKV, 1, D)
+        qb = O.seeded_bf16(3, 1, HQ, D)
+        lo, hi = shard.shard_range(rank, world, window)
+        st = O.OracleState(1, HKV, hi - lo, D)
+        n_old = shard.live_rows(rank, world, window, L)
+        if n_old:
+            O.kv_write(st, 0, 0, kb[:, lo:lo + n_old], vb[:, lo:lo + n_old])
+        plan = shard.resume_plan(P, world, window)                # every rank computes the same plan
+        if plan["owner"] == rank:                                # the owner of P writes the next row over dead data
+            O.kv_write(st, 0, P - lo, k2, v2)
+        n_live = shard.live_rows(rank, world, window, P + 1)
+        assert n_live == plan["live"][rank] + (1 if plan["owner"] == rank else 0)
+        m, l, acc = O.partial_rows_over_cache(st, 0, qb, P, n_live, key_offset=lo)
+        mine = torch.from_numpy(np.concatenate([m[0][:, None], l[0][:, None], acc[0]], axis=1))
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        if rank == 0:
+            parts = np.stack([t.numpy() for t in gathered], axis=1)
+            out_q.put(O.lse_merge(parts[:, :, 0], parts[:, :, 1], parts[:, :, 2:]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,L,P", [(2, 1900, 700), (4, 2000, 513), (4, 2000, 1024)])
+def test_resume_across_shard_boundary(world, L, P):
+    window = 2048
+    ctx = mp.get_context("spawn")
+    out_q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_resume_worker, args=(r, world, port, window, L, P, out_q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    merged = out_q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    kb, vb = O.seeded_bf16(1, HKV, L, D), O.seeded_bf16(2, HKV, L, D)
+    st = O.OracleState(1, HKV, window, D)
+    O.kv_write(st, 0, 0, kb, vb)                                 # the old sequence, L rows
+    want = O.decode_step_cpu(st, 0, O.seeded_bf16(3, 1, HQ, D), O.seeded_bf16(4, HKV, 1, D), O.seeded_bf16(5, HKV, 1, D), P)
+    np.testing.assert_allclose(merged, want[0], rtol=0, atol=3e-6)

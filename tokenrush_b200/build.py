@@ -1,6 +1,9 @@
 """Build libtrb_kv.so (the C-ABI CUDA library) in-tree for sm_100a with nvcc.
 
-    python -m tokenrush_b200.build [--force] [--verbose]
+    python -m tokenrush_b200.build [--force] [--verbose] [--timeline]
+
+--timeline builds a second, diagnostic library (libtrb_kv_timeline.so) whose decode kernel records
+per-CTA time stamps; `bench.py --workload timeline` loads it.
 
 The library has no dependency on torch or Python; the host package loads it with ctypes.
 """
@@ -23,26 +26,30 @@ def sources():
     return out
 
 
-def up_to_date() -> bool:
-    if not os.path.exists(LIB):
+def up_to_date(lib: str = LIB) -> bool:
+    if not os.path.exists(lib):
         return False
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(lib)
     return all(os.path.getmtime(s) <= t for s in sources())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and up_to_date():
-        return LIB
+LIB_TIMELINE = os.path.join(HERE, "libtrb_kv_timeline.so")
+
+
+def build(force: bool = False, verbose: bool = False, timeline: bool = False) -> str:
+    lib = LIB_TIMELINE if timeline else LIB
+    if not force and up_to_date(lib):
+        return lib
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB, os.path.join(CSRC, "trb_kv.cu")]
+    cmd = [nvcc] + NVCC_FLAGS + (["-DTRB_TIMELINE"] if timeline else []) + (["-Xptxas", "-v"] if verbose else []) + ["-o", lib, os.path.join(CSRC, "trb_kv.cu")]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
         raise RuntimeError("nvcc failed building libtrb_kv.so")
     if verbose:
         sys.stderr.write(r.stderr)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, timeline="--timeline" in sys.argv))

@@ -250,7 +250,8 @@ extern "C" int trb_kv_append(const trb_cache_t *cache, const void *k_src, const 
     Cursor pc = make_cursor(pos), nv = make_cursor(n_valid);
     cudaStream_t st = (cudaStream_t)stream;
     const int hv = n_valid != nullptr;
-    const int plan = pdl_plan_writer(st, c.k, pos, WrittenRange{nullptr, 0});
+    const AppendSource src = {k_src, v_src, (long long)src_head_stride, (long long)src_row_stride, (int)n_rows};
+    const int plan = pdl_plan_writer(st, c.k, pos, WrittenRange{nullptr, 0}, (n_valid || c.ring > 0) ? nullptr : &src);
     TRB_CUDA_CHECK(launch_kernel(c.d == 256 ? kv_append_kernel<256> : kv_append_kernel<128>, grid, dim3(32), 0, st, true, c,
                                  (const __nv_bfloat16 *)k_src, (const __nv_bfloat16 *)v_src, (long long)src_head_stride,
                                  (long long)src_row_stride, pc, nv, hv, (plan & PDL_TRIGGER_TOP) ? 1 : 0));
@@ -271,7 +272,7 @@ extern "C" int trb_attn_prep(const trb_cache_t *cache, const void *qkv, const vo
     dim3 grid(hq + c.hkv, m);
     Cursor pc = make_cursor(pos);
     cudaStream_t st = (cudaStream_t)stream;
-    const int plan = pdl_plan_writer(st, c.k, pos, WrittenRange{q_out, (size_t)m * hq * c.d * sizeof(__nv_bfloat16)});
+    const int plan = pdl_plan_writer(st, c.k, pos, WrittenRange{q_out, (size_t)m * hq * c.d * sizeof(__nv_bfloat16)}, nullptr);
     TRB_CUDA_CHECK(launch_kernel(c.d == 256 ? attn_prep_kernel<256> : attn_prep_kernel<128>, grid, dim3(32), 0, st, true, c,
                                  (const __nv_bfloat16 *)qkv, (const __nv_bfloat16 *)q_norm_w, (const __nv_bfloat16 *)k_norm_w,
                                  (const __nv_bfloat16 *)cos, (const __nv_bfloat16 *)sin, (long long)table_rows, (int)rotary_dim, eps,

@@ -30,6 +30,32 @@ static __device__ unsigned int g_status = 0;
 
 __device__ __forceinline__ void raise_status(unsigned int bits) { atomicOr(&g_status, bits); }
 
+// Optional per-CTA timeline of the decode kernels (a diagnostic build: -DTRB_TIMELINE).  Thread 0
+// of a CTA stamps %globaltimer at fixed points into shared memory and copies the stamps out when
+// the CTA leaves; the host reads them with trb_dbg_timeline().  The normal build compiles none of it.
+#ifdef TRB_TIMELINE
+constexpr int TL_SLOTS = 16, TL_CTAS = 256, TL_LAUNCHES = 64;
+static __device__ unsigned long long g_timeline[TL_LAUNCHES][TL_CTAS][TL_SLOTS];
+__device__ __forceinline__ unsigned long long tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRB_TL(buf, slot) do { if (threadIdx.x == 0) (buf)[slot] = tl_now(); } while (0)
+#define TRB_TL_SET(buf, slot, v) do { if (threadIdx.x == 0) (buf)[slot] = (unsigned long long)(v); } while (0)
+#define TRB_TL_FLUSH(buf, launch, cta)                                                                   \
+    do {                                                                                                  \
+        if (threadIdx.x == 0) {                                                                           \
+            (buf)[12] = tl_now();                                                                         \
+            for (int _i = 0; _i < TL_SLOTS; ++_i) g_timeline[(launch) % TL_LAUNCHES][(cta) % TL_CTAS][_i] = (buf)[_i]; \
+        }                                                                                                 \
+    } while (0)
+#else
+#define TRB_TL(buf, slot) do { } while (0)
+#define TRB_TL_SET(buf, slot, v) do { } while (0)
+#define TRB_TL_FLUSH(buf, launch, cta) do { } while (0)
+#endif
+
 // Cursor value = (dev ? *dev : 0) + host; the integer at dev is 4 or 8 bytes wide.
 struct Cursor {
     const void *dev;
@@ -201,14 +227,21 @@ enum PdlFlags : int {
     PDL_PRE_Q = 4,         // decode: the query rows are complete
     PDL_TRIGGER_TOP = 8,   // trigger the dependents before the first wait
     PDL_WAIT_FIRST = 16,   // append / prep: wait, then trigger
+    PDL_PRIVATE_WS = 32,   // decode: no launch in flight uses this workspace: partials and ticket need no wait,
+                           // and a CTA that merges no output row leaves without waiting
 };
 struct WrittenRange { const void *lo; size_t bytes; };
+// bf16 source rows of an append: element (head j, row i, dim x) at j * head_stride + i * row_stride + x
+struct AppendSource { const void *k, *v; long long head_stride, row_stride; int n_rows; };
 int pdl_mode();
-// a launch that writes rows of `cache_k` at `pos`.. (and `extra`, the q_out of attn_prep)
-int pdl_plan_writer(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, WrittenRange extra);
+// a launch that writes rows of `cache_k` at `pos`.. (and `extra`, the q_out of attn_prep); `src`: the
+// rows of a plain append (nullptr for attn_prep, whose K rows are not its input rows)
+int pdl_plan_writer(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, WrittenRange extra, const AppendSource *src);
 // a decode of `cache_k` at `pos` reading `q`, writing `out[0..2]`
-int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, int new_rows, WrittenRange q,
-                    const WrittenRange (&out)[3]);
+// `fresh` <- the source rows of the one append in flight on this cache, when the decode may take its
+// m new rows from there instead of waiting for them in the cache (fresh->k == nullptr otherwise)
+int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, int new_rows, int m, WrittenRange q,
+                    const WrittenRange (&out)[3], const void *workspace, AppendSource *fresh);
 // an ordinary launch of the library on `st`: everything before it completes before anything after it starts
 void pdl_note_fence(cudaStream_t st);
 

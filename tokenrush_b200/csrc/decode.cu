@@ -38,13 +38,12 @@
 namespace trb {
 
 constexpr int DEC_BN = 32;                       // keys per pipeline stage = one unit of work
-constexpr int DEC_CONSUMERS = 12;                // consumer warps per CTA
-constexpr int DEC_CTHREADS = DEC_CONSUMERS * 32;
-constexpr int DEC_THREADS = DEC_CTHREADS;        // no dedicated producer: slice-0 warps issue their group's loads
+constexpr int DEC_CONSUMERS = 12;                // warps per CTA (all consume; the slice-0 warps also issue their stream's loads)
+constexpr int DEC_HALF_WARPS = 6;                // ... of the half-size CTA, two of which fit one SM (see launch_decode)
 constexpr int DEC_MAX_ROWS = 48;                 // (hq / hkv) * m
 constexpr int DEC_MAX_NT = DEC_MAX_ROWS / 8;
 constexpr int DEC_MIN_TILES = 4;                 // a split is not made smaller than this
-constexpr int DEC_STAGE_BYTES_TOTAL = 192 * 1024;
+constexpr int DEC_STAGE_BYTES_PER_WARP = 16 * 1024;   // pipeline stages: 192 KB for 12 warps, 96 KB for 6
 constexpr int DEC_MAX_SPLITS = 148;              // bounds the tail's weight table in shared memory
 constexpr int DEC_EPI_PAD = 4;                   // floats of padding per staged output row
 
@@ -64,6 +63,10 @@ struct DecodeParams {
     long long max_len, ring, shard_lo;
     int sharded;
     int pdl_flags;                // PDL_*: what this launch may touch before its dependency wait
+    // rows pos .. pos + m - 1 taken from the source rows of the append that is still writing them
+    // (fresh_k == nullptr: they are read from the cache like every other row)
+    const __nv_bfloat16 *fresh_k, *fresh_v;
+    long long fresh_hs, fresh_rs; // element strides of the source: head, row
     unsigned long long *word;     // [hkv] ticket words: launch epoch << 16 | CTAs arrived
     uint4 *part_ml;               // [hkv][nsplit][rows_pad] (max, tag, sum, tag)
     uint2 *part_acc;              // [hkv][nsplit][rows_pad][D] (value, tag)
@@ -72,26 +75,28 @@ struct DecodeParams {
     int p2p_world, p2p_rank;      // p2p_world == 0: no exchange
 };
 
-template <int D, bool FP8>
+template <int D, bool FP8, int NW = DEC_CONSUMERS>
 struct DecodeCfg {
+    static constexpr int MAXNT = NW == DEC_CONSUMERS ? DEC_MAX_NT : 1;   // the half-size CTA serves one 8-row slice (M = 1)
     static constexpr int ROWB = D * (FP8 ? 1 : 2);
     static constexpr int SEGS = ROWB / 128;
     static constexpr int TILE = DEC_BN * ROWB;
-    static constexpr int NSTAGE_RAW = DEC_STAGE_BYTES_TOTAL / (2 * TILE);
+    static constexpr int NSTAGE_RAW = NW * DEC_STAGE_BYTES_PER_WARP / (2 * TILE);
     static constexpr int NSTAGE = NSTAGE_RAW > 16 ? 16 : NSTAGE_RAW;
     static constexpr int NCP = ROWB / 32;                        // 32-byte chunk pairs per row
     static constexpr int ACC = FP8 ? NCP * 2 : NCP;              // m16n8 accumulator tiles
     static constexpr int QF_WORDS = FP8 ? 4 : 2;                 // query-fragment words per (slice, cp, lane)
     static constexpr int SCALE_OFF = NSTAGE * 2 * TILE;          // [NSTAGE][2][BN] floats
     static constexpr int BAR_OFF = SCALE_OFF + NSTAGE * 2 * DEC_BN * 4;
-    static constexpr int QF_OFF = BAR_OFF + 2 * NSTAGE * 8;      // [DEC_MAX_NT][NCP][32][QF_WORDS] words
-    static constexpr int QF_BYTES = DEC_MAX_NT * NCP * 32 * QF_WORDS * 4;
+    static constexpr int QF_OFF = BAR_OFF + 2 * NSTAGE * 8;      // [MAXNT][NCP][32][QF_WORDS] words
+    static constexpr int QF_BYTES = MAXNT * NCP * 32 * QF_WORDS * 4;
     static constexpr int MISC_OFF = QF_OFF + QF_BYTES;
-    static constexpr int ML_BYTES = DEC_CONSUMERS * 8 * 2 * 4;   // per-warp (max, sum) of 8 columns
-    static constexpr int QINV_OFF = MISC_OFF + ML_BYTES;         // [DEC_MAX_NT][8] floats
-    static constexpr int FLAG_OFF = QINV_OFF + DEC_MAX_NT * 8 * 4;
-    static constexpr int SMEM = FLAG_OFF + 64 + 1024;            // + slack to align the base
-    static_assert(SMEM <= 227 * 1024, "shared memory budget");
+    static constexpr int ML_BYTES = NW * 8 * 2 * 4;              // per-warp (max, sum) of 8 columns
+    static constexpr int QINV_OFF = MISC_OFF + ML_BYTES;         // [MAXNT][8] floats
+    static constexpr int FLAG_OFF = QINV_OFF + MAXNT * 8 * 4;
+    static constexpr int TL_OFF = FLAG_OFF + 64;                 // timeline stamps (diagnostic build only)
+    static constexpr int SMEM = TL_OFF + 128 + 1024;             // + slack to align the base
+    static_assert(SMEM <= (NW == DEC_CONSUMERS ? 227 : 113) * 1024, "shared memory budget (two half-size CTAs per SM)");
 };
 
 // Byte offset of (row, byte_in_row) inside a K or V tile in shared memory.  A tile is stored as
@@ -165,9 +170,12 @@ __device__ __forceinline__ bool poll_tagged(const uint4 *src, const unsigned int
 // on their way to the workspace and sm_flag is visible.  `smem` is scratch from its start (at
 // least 16 KB) once every thread has passed the barrier below.
 template <int D, int NTHREADS>
-__device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem, const int *sm_flag, const int j, const int active) {
+__device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem, const int *sm_flag, const int j, const int active,
+                                            unsigned long long *tl = nullptr) {
+    (void)tl;
     const int helper = sm_flag[0];
     if (helper < 0) return;
+    TRB_TL(tl, 9);
     const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
     const int tid = threadIdx.x, lane = threadIdx.x & 31;
     constexpr int ITEMS = D / 4, GROUPS = NTHREADS / ITEMS;
@@ -189,8 +197,46 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
     float *sm_l = sm_m + (DEC_MAX_SPLITS + 4);                          // [n_parts]
     float4 *sm_red = reinterpret_cast<float4 *>(reinterpret_cast<float *>(smem) + 4 * (DEC_MAX_SPLITS + 4)) +
                      (in_team ? team : 0) * gt * ITEMS;                 // [gt][ITEMS] per team
-    constexpr int PRE = 8;                                              // splits per thread requested together
+    constexpr int PRE = NTHREADS >= 384 ? 8 : 13;                       // splits per thread requested together
     bool all_ok = true;
+
+    // ---- the m rows that the append of this step is still writing, from its source rows: quantised
+    // and dequantised exactly as the append does (tokenrush/fused.py:336-340), kept as fp32 rows of
+    // this kv head in shared memory.  They enter the merge below as one more partial.
+    float *fr_k = reinterpret_cast<float *>(smem + 16384);              // [8][D]
+    float *fr_v = fr_k + 8 * D;                                         // [8][D]
+    float *fr_s = fr_v + 8 * D;                                         // [2 teams][8] scores, log2 units
+    int *fr_held = reinterpret_cast<int *>(fr_s + 16);                  // [8] this cache holds the row's position
+    const int n_fresh = p.fresh_k ? p.m : 0;
+    if (n_fresh) {
+        __syncthreads();                                                // the CTA's own partial has left shared memory
+        const long long pos = load_cursor(p.pos);
+        constexpr int EPL = D / 32;
+        for (int r = tid >> 5; r < n_fresh; r += NTHREADS / 32) {
+            const long long loc = pos + r - p.shard_lo;
+            for (int which = 0; which < 2; ++which) {
+                const __nv_bfloat16 *src = (which ? p.fresh_v : p.fresh_k) + (long long)j * p.fresh_hs + (long long)r * p.fresh_rs;
+                float f[EPL];
+                __nv_bfloat16 raw[EPL];
+                load_row<EPL>(src, lane, f, raw);
+                if (p.ks) {
+                    float amax = 0.f;
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) amax = fmaxf(amax, fabsf(f[e]));
+                    amax = warp_max(amax);
+                    const float sc = __fdiv_rn(fmaxf(amax, 1e-6f), 448.0f);
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) {
+                        const __nv_fp8_storage_t code = __nv_cvt_float_to_fp8(__fdiv_rn(f[e], sc), __NV_SATFINITE, __NV_E4M3);
+                        f[e] = __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3))) * sc;
+                    }
+                }
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) (which ? fr_v : fr_k)[r * D + lane * EPL + e] = f[e];
+            }
+            if (lane == 0) fr_held[r] = (p.ring > 0 || (loc >= 0 && loc < p.max_len)) ? 1 : 0;
+        }
+    }
     for (int c = helper; c < nclaims; c += helpers) {
         __syncthreads();                                                // the shared memory below is free (first claim: the CTA's own partial has left it)
         const int row = c * rc + team;
@@ -221,14 +267,39 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
                 }
                 sm_m[sp] = v.x; sm_l[sp] = v.y;
             }
+        if (n_fresh && row_on) {                                        // scores of this row against the fresh keys, one warp per key
+            constexpr int EPL = D / 32;
+            const __nv_bfloat16 *qp = p.q + grow * D + lane * EPL;
+            for (int r = ttid >> 5; r < n_fresh; r += team_threads / 32) {
+                float dot = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) dot = fmaf(__bfloat162float(qp[e]), fr_k[r * D + lane * EPL + e], dot);
+                dot = warp_sum(dot);
+                if (lane == 0) fr_s[team * 8 + r] = dot * p.scale_log2;
+            }
+        }
         __syncthreads();
+        TRB_TL(tl, 10);
         float mmax = -INFINITY, lsum = 0.f;
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
         if (row_on) {
             for (int sp = lane; sp < n_parts; sp += 32) mmax = fmaxf(mmax, sm_m[sp]);
             mmax = warp_max(mmax);
+            // fresh keys 0..qi are visible to query row qi (tokenrush/fused.py:382: keys <= pos + qi)
+            const int n_vis = n_fresh ? (qi + 1 < n_fresh ? qi + 1 : n_fresh) : 0;
+            for (int r = 0; r < n_vis; ++r)
+                if (fr_held[r]) mmax = fmaxf(mmax, fr_s[team * 8 + r]);
             for (int sp = lane; sp < n_parts; sp += 32) lsum += sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax) * sm_l[sp];
             lsum = warp_sum(lsum);
+            for (int r = 0; r < n_vis; ++r)
+                if (fr_held[r]) {
+                    const float w = fast_exp2(fr_s[team * 8 + r] - mmax);
+                    lsum += w;
+                    if (tgrp == 0) {
+                        const float4 v = *reinterpret_cast<const float4 *>(&fr_v[r * D + d4]);
+                        o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+                    }
+                }
             for (int sp0 = tgrp; sp0 < active; sp0 += PRE * gt) {         // split order within the group: ascending
                 if (sp0 != tgrp) {
 #pragma unroll
@@ -258,6 +329,7 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
             sm_red[tgrp * ITEMS + item] = o;
         }
         __syncthreads();
+        TRB_TL(tl, 11);
         const bool lead = row_on && tgrp == 0;                           // these threads hold the row from here on
         if (lead) {
             for (int k = 1; k < gt; ++k) {
@@ -265,6 +337,10 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
                 o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
             }
         }
+        // Outputs (and the exchange with other GPUs) only once every earlier launch is complete.  The
+        // helpers are the CTAs of a launch that always wait, so a launch never completes before
+        // the launches it follows; with a private workspace the other CTAs have left without waiting.
+        pdl_wait();
         if (p.shard_acc) {
             if (lead) {
                 *reinterpret_cast<float4 *>(&p.shard_acc[grow * D + d4]) = o;
@@ -367,10 +443,11 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
 
 namespace trb {
 
-template <int D, bool FP8, int GS>
-__global__ void __launch_bounds__(DEC_THREADS, 1)
+template <int D, bool FP8, int GS, int NW>
+__global__ void __launch_bounds__(NW * 32, NW == DEC_CONSUMERS ? 1 : 2)
 decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
-    using C = DecodeCfg<D, FP8>;
+    using C = DecodeCfg<D, FP8, NW>;
+    constexpr int DEC_CTHREADS = NW * 32;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     float *sm_scale = reinterpret_cast<float *>(smem + C::SCALE_OFF);
@@ -380,9 +457,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     float *sm_ml = reinterpret_cast<float *>(smem + C::MISC_OFF);                 // [12][8][2]
     float *sm_qinv = reinterpret_cast<float *>(smem + C::QINV_OFF);               // [6][8]
     int *sm_flag = reinterpret_cast<int *>(smem + C::FLAG_OFF);
+    unsigned long long *sm_tl = reinterpret_cast<unsigned long long *>(smem + C::TL_OFF);
+    (void)sm_tl;
 
     const int split = blockIdx.x, j = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TRB_TL(sm_tl, 0);
 
     // ---- dependency plan: what may be touched before the wait was decided on the host -----
     const int flags = p.pdl_flags;
@@ -492,7 +572,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
             next_issue += p.kw;
         }
     };
+    TRB_TL(sm_tl, 1);
     if (issuer) issue_more(C::NSTAGE);
+    TRB_TL(sm_tl, 2);
     if (!(flags & PDL_PRE_Q)) {                                // the query rows may come from the launch before this one
         dep_wait();
         if (issuer) issue_more(C::NSTAGE);                     // ... and every row of the cache is complete now
@@ -545,6 +627,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     }
     __syncthreads();
 
+    TRB_TL(sm_tl, 3);
     const uint32_t *qf = sm_qf + (size_t)nt_idx * C::NCP * 32 * C::QF_WORDS + lane * C::QF_WORDS;
 
     // Visibility window of this lane's two query columns, in virtual rows of this cache
@@ -594,6 +677,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
                 issue_more(i + C::NSTAGE);
             }
             if (!pipe_ok || !mbar_wait(&bar_full[s], (i / C::NSTAGE) & 1)) break;
+            if (i == 0) TRB_TL(sm_tl, 4);
             const int key0 = (t0 + i) * DEC_BN;                                    // virtual row of the tile
             if (key0 + gb < lloc_i && key0 + gb + 16 * GS - 1 >= row_lo_i) {
                 const uint32_t kt = smem_u32(smem + s * 2 * C::TILE);
@@ -769,12 +853,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     // Everything from here on touches the workspace and the outputs: the launches before this one
     // must be complete.  One thread takes the kv head's ticket right away, so that its round trip
     // runs under the merge below.
-    dep_wait();
+    TRB_TL(sm_tl, 5);
+    // (with a workspace that no launch in flight uses, the partial needs no wait: only the CTAs that
+    // merge output rows wait, in the tail, before they write them)
+    const bool ws_private = (flags & PDL_PRIVATE_WS) != 0;
+    if (!ws_private) dep_wait();
+    TRB_TL(sm_tl, 6);
     unsigned long long ticket = 0ull;
     if (threadIdx.x == 0) ticket = decode_ticket_take(p, j);
     // 1. merge the warps that share an 8-row slice (fixed order) through shared memory: every warp
     // stages its accumulators unscaled, together with its (max, sum); the reducing threads weigh them
     __syncthreads();                    // every stage has been consumed
+    TRB_TL(sm_tl, 7);
     if (warp_on && g == 0) {
         sm_ml[(warp * 8 + 2 * t + 0) * 2 + 0] = mx[0]; sm_ml[(warp * 8 + 2 * t + 0) * 2 + 1] = ls[0];
         sm_ml[(warp * 8 + 2 * t + 1) * 2 + 0] = mx[1]; sm_ml[(warp * 8 + 2 * t + 1) * 2 + 1] = ls[1];
@@ -814,7 +904,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
         if (d4 == 0) st_volatile_v4(p.part_ml + part_base + row, make_uint4(__float_as_uint(mg), tag, __float_as_uint(lg), tag));
     }
 
-    decode_tail<D, DEC_CTHREADS>(p, smem, sm_flag, j, active);
+    TRB_TL(sm_tl, 8);
+    TRB_TL_SET(sm_tl, 13, sm_flag[0]);
+    TRB_TL_SET(sm_tl, 14, my_tiles);
+    decode_tail<D, DEC_CTHREADS>(p, smem, sm_flag, j, active, sm_tl);
+    TRB_TL_FLUSH(sm_tl, (unsigned int)sm_flag[2], j * p.nsplit + split);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -924,18 +1018,20 @@ static WorkspaceLayout workspace_layout(int hkv, int nsplit, int rows_pad, int d
     return w;
 }
 
-template <int D, bool FP8, int GS>
+template <int D, bool FP8, int GS, int NW>
 static int launch_decode_gs(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, cudaStream_t st) {
-    using C = DecodeCfg<D, FP8>;
+    using C = DecodeCfg<D, FP8, NW>;
     static bool attr_set[64] = {};
     int dev = 0;
     TRB_CUDA_CHECK(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        TRB_CUDA_CHECK(cudaFuncSetAttribute(decode_kernel<D, FP8, GS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        TRB_CUDA_CHECK(cudaFuncSetAttribute(decode_kernel<D, FP8, GS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        TRB_CUDA_CHECK(cudaFuncSetAttribute(decode_kernel<D, FP8, GS, NW>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                            cudaSharedmemCarveoutMaxShared));
         attr_set[dev & 63] = true;
     }
     dim3 grid(p.nsplit, p.hkv);
-    TRB_CUDA_CHECK(launch_kernel(decode_kernel<D, FP8, GS>, grid, dim3(DEC_THREADS), (size_t)C::SMEM, st, true, mk, mv, p));
+    TRB_CUDA_CHECK(launch_kernel(decode_kernel<D, FP8, GS, NW>, grid, dim3(NW * 32), (size_t)C::SMEM, st, true, mk, mv, p));
     return TRB_OK;
 }
 
@@ -944,9 +1040,21 @@ static int launch_decode_gs(const CUtensorMap &mk, const CUtensorMap &mv, const 
 // and the tensor pipe; there a warp takes whole 32-key tiles (one softmax step per 32 keys).
 static int decode_groups_per_warp(int nt) { return nt == 1 ? 1 : 2; }
 
+// A decode that runs inside a chain of library launches (it releases its dependents at its top)
+// and has one slice takes half-size CTAs: 6 warps and 96 KB of stages, so that two CTAs fit one
+// SM.  The grid stays one CTA per SM: the second slot of every SM is taken by the CTA of the next
+// layer's launch, whose prologue (cursor, descriptors, first tiles, under load several
+// microseconds) and epilogue then run beside this launch's streaming instead of leaving the SM
+// idle.  A launch that runs alone keeps the full-size CTA (all 192 KB in flight are its own).
+static int decode_warps(const DecodeParams &p) {
+    return (p.nt == 1 && (p.pdl_flags & PDL_TRIGGER_TOP)) ? DEC_HALF_WARPS : DEC_CONSUMERS;
+}
+
 template <int D, bool FP8>
 static int launch_decode(const CUtensorMap &mk, const CUtensorMap &mv, const DecodeParams &p, cudaStream_t st) {
-    return decode_groups_per_warp(p.nt) == 2 ? launch_decode_gs<D, FP8, 2>(mk, mv, p, st) : launch_decode_gs<D, FP8, 1>(mk, mv, p, st);
+    if (decode_groups_per_warp(p.nt) == 2) return launch_decode_gs<D, FP8, 2, DEC_CONSUMERS>(mk, mv, p, st);
+    return decode_warps(p) == DEC_HALF_WARPS ? launch_decode_gs<D, FP8, 1, DEC_HALF_WARPS>(mk, mv, p, st)
+                                              : launch_decode_gs<D, FP8, 1, DEC_CONSUMERS>(mk, mv, p, st);
 }
 
 // Query rows per kv head (heads per kv head x M) from which the tensor-core kernel takes FP8
@@ -1017,7 +1125,7 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     p.gate_rs = a->gate_row_stride; p.gate_hs = a->gate_head_stride;
     p.ks = c.k_scale; p.vs = c.v_scale;
     p.m = a->m; p.hq = a->hq; p.hkv = c.hkv; p.g = g; p.rows = rows;
-    p.nt = (rows + 7) / 8; p.kw = DEC_CONSUMERS / (p.nt * (2 / decode_groups_per_warp(p.nt)));
+    p.nt = (rows + 7) / 8; p.kw = 0;                              // kw: set once the launch plan is known
     p.nsplit = decode_nsplit(c.hkv); p.rows_pad = p.nt * 8;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.new_rows = a->new_rows ? 1 : 0; p.window = a->window; p.n_extra = a->n_extra;
@@ -1052,10 +1160,16 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     const WrittenRange outs[3] = {{a->out, a->out ? out_rows * c.d * sizeof(__nv_bfloat16) : 0},
                                   {a->partial_ml, a->partial_ml ? out_rows * 2 * sizeof(float) : 0},
                                   {a->partial_acc, a->partial_acc ? out_rows * c.d * sizeof(float) : 0}};
-    p.pdl_flags = pdl_plan_decode(st, c.k, &a->pos, p.new_rows, WrittenRange{a->q, out_rows * c.d * sizeof(__nv_bfloat16)}, outs);
+    AppendSource fresh;
+    p.pdl_flags = pdl_plan_decode(st, c.k, &a->pos, p.new_rows, a->m, WrittenRange{a->q, out_rows * c.d * sizeof(__nv_bfloat16)}, outs,
+                                  a->workspace, &fresh);
+    p.fresh_k = (const __nv_bfloat16 *)fresh.k; p.fresh_v = (const __nv_bfloat16 *)fresh.v;
+    p.fresh_hs = fresh.head_stride; p.fresh_rs = fresh.row_stride;
+    if (p.fresh_k) p.new_rows = 0;                            // the scan covers the rows below the cursor, all visible to every row
     // a ring cache maps several positions to one row: the rows below the cursor are not the rows
     // below the in-flight append
-    if (c.ring > 0 && !(p.pdl_flags & PDL_ALL_STABLE)) p.pdl_flags &= PDL_TRIGGER_TOP;
+    if (c.ring > 0 && !(p.pdl_flags & PDL_ALL_STABLE)) p.pdl_flags &= (PDL_TRIGGER_TOP | PDL_PRIVATE_WS);
+    p.kw = decode_warps(p) / (p.nt * (2 / decode_groups_per_warp(p.nt)));
     if (tensor_kernel) return launch_decode_tc(mk, mv, p, st);
     if (c.d == 256) return c.fp8 ? launch_decode<256, true>(mk, mv, p, st) : launch_decode<256, false>(mk, mv, p, st);
     return c.fp8 ? launch_decode<128, true>(mk, mv, p, st) : launch_decode<128, false>(mk, mv, p, st);
@@ -1155,3 +1269,14 @@ extern "C" int trb_attn_decode_static(const trb_cache_t *cache, const trb_decode
     a.workspace_bytes = TRB_STATIC_SCRATCH_BYTES;
     return trb_attn_decode(cache, &a, stream);
 }
+
+#ifdef TRB_TIMELINE
+// Diagnostic build only: copy the per-CTA timeline stamps of the last TL_LAUNCHES decode launches
+// ([launch % 64][cta][16] nanosecond stamps of %globaltimer) to the host.  Synchronises the device.
+extern "C" int trb_dbg_timeline(void *host_out, size_t bytes) {
+    if (!host_out || bytes < sizeof(unsigned long long) * TL_LAUNCHES * TL_CTAS * TL_SLOTS) return TRB_E_ARG;
+    TRB_CUDA_CHECK(cudaDeviceSynchronize());
+    TRB_CUDA_CHECK(cudaMemcpyFromSymbol(host_out, trb::g_timeline, sizeof(unsigned long long) * TL_LAUNCHES * TL_CTAS * TL_SLOTS));
+    return TRB_OK;
+}
+#endif

@@ -238,8 +238,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
             if (i >= TC_VSLOTS && !mbar_wait(&v_free[i % TC_VSLOTS], ((i / TC_VSLOTS) & 1) ^ 1)) break;
             issue_v(i);
         }
-        // this warp is idle from here on: it takes the kv head's ticket (workspace: after the wait)
-        dep_wait();
+        // this warp is idle from here on: it takes the kv head's ticket (a workspace that an earlier
+        // launch may still use: after the wait)
+        if (!(flags & PDL_PRIVATE_WS)) dep_wait();
         if (lane == 0) decode_ticket(p, j, active, NTHREADS / (D / 4), sm_flag, decode_ticket_take(p, j));
         named_barrier(15, NTHREADS);
     } else if (warp == W_MMA) {
@@ -445,7 +446,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         ok = !dead;
         if (ok && my_tiles > 0) ok = mbar_wait(&pv_done[(my_tiles - 1) & 1], ((my_tiles - 1) >> 1) & 1);
         tc_fence_after();
-        dep_wait();                                                            // the workspace belongs to this launch now
+        if (!(flags & PDL_PRIVATE_WS)) dep_wait();                             // the workspace belongs to this launch now
         named_barrier(15, NTHREADS);                                           // the ticket (taken by the producer warp) is in sm_flag
         const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
         const long long part_base = ((long long)j * p.nsplit + split) * p.rows_pad;
@@ -514,7 +515,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                            make_uint4(__float_as_uint(((unset >> kl) & 1u) ? -INFINITY : 7.f - cr), tag, __float_as_uint(l), tag));
         }
     }
-    dep_wait();
+    if (!(flags & PDL_PRIVATE_WS)) dep_wait();
     __syncthreads();
     if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TC_TMEM_COLS); }
     decode_tail<D, NTHREADS>(p, smem, sm_flag, j, active);

@@ -35,6 +35,8 @@ struct InFlight {
     const void *cur_dev;          // ... at this cursor
     long long cur_host;
     WrittenRange w[3];            // other memory it writes (q_out of attn_prep, outputs of a decode)
+    const void *ws;               // decode workspace it uses (nullptr: none)
+    AppendSource src;             // source rows of a plain append (k == nullptr: none)
 };
 struct StreamTrack {
     std::vector<InFlight> s;      // library launches that may still be running when the next one starts
@@ -72,12 +74,13 @@ bool overlaps(const WrittenRange &a, const WrittenRange &b) {
 }
 }  // namespace
 
-int pdl_plan_writer(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, WrittenRange extra) {
+int pdl_plan_writer(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, WrittenRange extra, const AppendSource *src) {
     const int mode = pdl_mode();
     if (mode == 0) return PDL_WAIT_FIRST;
     std::lock_guard<std::mutex> lock(g_track_mu);
     StreamTrack &t = track_of(st);
-    InFlight me = {cache_k, pos ? pos->dev : nullptr, pos ? pos->host : 0, {extra, {nullptr, 0}, {nullptr, 0}}};
+    InFlight me = {cache_k, pos ? pos->dev : nullptr, pos ? pos->host : 0, {extra, {nullptr, 0}, {nullptr, 0}}, nullptr,
+                   src ? *src : AppendSource{nullptr, nullptr, 0, 0, 0}};
     // Triggering before the wait is harmless for this kernel (it reads its inputs after its wait);
     // whoever starts because of it decides from the list what it may touch.  The first launch
     // of a chain waits first, so that everything before the chain is complete for all of it.
@@ -87,9 +90,10 @@ int pdl_plan_writer(cudaStream_t st, const void *cache_k, const trb_cursor_t *po
     return chained ? PDL_TRIGGER_TOP : PDL_WAIT_FIRST;
 }
 
-int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, int new_rows, WrittenRange q,
-                    const WrittenRange (&out)[3]) {
+int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *pos, int new_rows, int m, WrittenRange q,
+                    const WrittenRange (&out)[3], const void *workspace, AppendSource *fresh) {
     const int mode = pdl_mode();
+    *fresh = AppendSource{nullptr, nullptr, 0, 0, 0};
     if (mode == 0) return 0;
     std::lock_guard<std::mutex> lock(g_track_mu);
     StreamTrack &t = track_of(st);
@@ -98,8 +102,14 @@ int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *po
     // and becomes the point before which everything is complete.
     if (!t.s.empty() && t.s.size() < MAX_IN_FLIGHT) {
         int writers = 0;
-        bool same_rows = true, q_clean = true;
+        bool same_rows = true, q_clean = true, ws_free = true;
+        const InFlight *writer = nullptr;
         for (const InFlight &e : t.s) {
+            if (e.cache_k && e.cache_k == cache_k) writer = &e;
+            if (e.ws && e.ws == workspace) ws_free = false;
+            for (const WrittenRange &w : e.w)                  // an output of this launch that an earlier one still writes
+                for (const WrittenRange &o : out)
+                    if (overlaps(w, o)) ws_free = false;
             if (e.cache_k && e.cache_k == cache_k) {
                 ++writers;
                 // the rows in flight must be the ones this decode expects at its cursor
@@ -113,9 +123,21 @@ int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *po
             if (writers == 0) flags |= PDL_ALL_STABLE;
             if (q_clean) flags |= PDL_PRE_Q;
             if (mode == 2) flags |= PDL_TRIGGER_TOP;
+            if (mode == 2 && ws_free) flags |= PDL_PRIVATE_WS;
+            // In a chain, the m rows of the one append in flight need not be awaited in the cache: the
+            // decode quantises them from the append's own source rows (same arithmetic, same values)
+            // and merges them as one more partial, while the scan covers the rows below the cursor.
+            if (mode == 2 && writers == 1 && writer->src.k && writer->src.n_rows == m) {
+                bool src_clean = true;                           // nobody in flight writes the source rows
+                const WrittenRange sk = {writer->src.k, (size_t)1}, sv = {writer->src.v, (size_t)1};
+                for (const InFlight &e : t.s)
+                    for (const WrittenRange &w : e.w)
+                        if (overlaps(w, sk) || overlaps(w, sv)) src_clean = false;
+                if (src_clean) { *fresh = writer->src; flags |= PDL_ALL_STABLE; }
+            }
         }
     }
-    InFlight me = {nullptr, nullptr, 0, {out[0], out[1], out[2]}};
+    InFlight me = {nullptr, nullptr, 0, {out[0], out[1], out[2]}, workspace, AppendSource{nullptr, nullptr, 0, 0, 0}};
     if (!(flags & PDL_TRIGGER_TOP)) t.s.clear();      // it triggers after its wait: only it is in flight afterwards
     t.s.push_back(me);
     return flags;

@@ -75,23 +75,38 @@ def set_launch_mode(mode: int):
     L.check(L.lib().trb_set_programmatic_launch(int(mode)), "trb_set_programmatic_launch")
 
 
-def _workspace(device, hq: int, hkv: int, d: int) -> torch.Tensor:
-    """Split-partial scratch + ticket words, one per (device, stream, geometry), zeroed once.
-    Calls that share it are ordered by the stream."""
-    key = (device.index, _stream(), hq, hkv, d)
-    ws = _workspaces.get(key)
-    if ws is None:
+WORKSPACE_SLOTS = 16       # decode workspaces per (device, stream, geometry), used in rotation
+
+
+def _workspace(device, hq: int, hkv: int, d: int, m: int):
+    """Split-partial scratch + ticket words for one decode call: (device pointer, bytes).  Every
+    (device, stream, geometry) owns WORKSPACE_SLOTS workspaces, zeroed once, and hands them out in
+    rotation: consecutive decode calls of a step then never share one, which lets a call in a
+    chain of library launches (launch mode 2) publish its partials without waiting for the call
+    before it.  Calls that get the same slot are ordered by the stream."""
+    key = (device.index, _stream(), hq, hkv, d, m)
+    ent = _workspaces.get(key)
+    if ent is None:
         if torch.cuda.is_current_stream_capturing():
-            # a zero-fill recorded into the graph would wipe the launch count at every replay
-            raise RuntimeError("the first decode call of a (device, stream, geometry) allocates and zeroes its workspace: "
+            # a zero-fill recorded into the graph would wipe the launch counts at every replay
+            raise RuntimeError("the first decode call of a (device, stream, geometry) allocates and zeroes its workspaces: "
                                "make it outside graph capture (run the step once on the capture stream first)")
-        g = hq // hkv
-        n = L.lib().trb_decode_workspace_bytes(hq, hkv, d, max(1, 48 // g))
+        n = L.lib().trb_decode_workspace_bytes(hq, hkv, d, m)
         if n == 0:
-            raise ValueError(f"unsupported geometry hq={hq} hkv={hkv} d={d}")
-        ws = torch.zeros(n, device=device, dtype=torch.uint8)
-        _workspaces[key] = ws
-    return ws
+            raise ValueError(f"unsupported geometry hq={hq} hkv={hkv} d={d} m={m}")
+        n = (n + 255) // 256 * 256
+        ent = [torch.zeros(WORKSPACE_SLOTS * n, device=device, dtype=torch.uint8), n, 0]
+        _workspaces[key] = ent
+    buf, n, count = ent
+    ent[2] = count + 1
+    return buf.data_ptr() + (count % WORKSPACE_SLOTS) * n, n
+
+
+def workspace_tensor(device, hq: int, hkv: int, d: int, m: int):
+    """The tensor that holds the WORKSPACE_SLOTS workspaces of the current stream for this geometry
+    (None before the first decode call); zero it after a call reported a workspace problem."""
+    ent = _workspaces.get((device.index, _stream(), hq, hkv, d, m))
+    return None if ent is None else ent[0]
 
 
 # ------------------------------------------------------------------------------ append
@@ -153,14 +168,14 @@ def _decode(q, k_cache, v_cache, pos, HQ, HKV, D, k_scale, v_scale, *, gate=None
         raise ValueError("q must be contiguous bf16 [M, HQ*D]")
     M = q.shape[0]
     cache = _cache(k_cache, v_cache, k_scale, v_scale, ring, shard_lo)
-    ws = _workspace(q.device, HQ, HKV, D)
+    ws_ptr, ws_bytes = _workspace(q.device, HQ, HKV, D, M)
     a = L.DecodeArgs()
     a.q = q.data_ptr()
     a.m, a.hq = M, HQ
     a.scale = float(D ** -0.5 if scale is None else scale)
     a.new_rows, a.window = int(new_rows), int(window)
     a.pos = _cursor(pos)
-    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.workspace, a.workspace_bytes = ws_ptr, ws_bytes
     if gate is not None:
         a.gate, a.gate_row_stride, a.gate_head_stride = gate, gate_rs, gate_hs
     if extra is not None:

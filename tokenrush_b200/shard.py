@@ -48,6 +48,39 @@ def live_rows(rank: int, world: int, window: int, live: int, headroom: int = 0) 
     return max(0, min(live - lo, cap))
 
 
+def resume_plan(pos: int, world: int, window: int, headroom: int = 0) -> dict:
+    """What resuming a sharded sequence at position `pos` (a prefix-reuse restore or a rewind after
+    rejected drafts: tokenrush/session.py:92-103, tokenrush/mtp.py:84-87) means for every rank.  The
+    cursor is replicated, so every rank sets the same value; nothing in any cache moves:
+
+      owner  - the rank that holds position `pos`, i.e. the one whose append writes the next row;
+      live   - live rows per rank afterwards (rank r keeps min(max(pos - lo_r, 0), rows_r));
+      dead   - rows per rank that held positions >= pos of the old sequence and are dead data from
+               now on (given the old live length `old_live` via resume_rows_dropped); they are
+               overwritten by later appends, as the rejected rows of a verify step are.
+    A rewind across a shard boundary therefore empties the later ranks completely (live 0: their
+    kernels see no tile and publish an empty partial) and shortens the owner's shard."""
+    if not 0 <= pos <= window + headroom:
+        raise ValueError(f"position {pos} outside the sharded sequence (window {window} + headroom {headroom})")
+    return {"pos": pos, "owner": owner_of(pos, world, window),
+            "live": [live_rows(r, world, window, pos, headroom) for r in range(world)]}
+
+
+def resume_rows_dropped(old_live: int, pos: int, world: int, window: int, headroom: int = 0) -> list:
+    """Rows per rank that stop being live when a sequence of `old_live` positions resumes at `pos`."""
+    return [live_rows(r, world, window, old_live, headroom) - live_rows(r, world, window, min(pos, old_live), headroom)
+            for r in range(world)]
+
+
+def ring_snapshot_valid(snap_pos: int, cur_pos: int, ring: int, window: int, block: int) -> bool:
+    """Can a snapshot taken at `snap_pos` still be resumed when the draft's ring cache has been
+    written up to `cur_pos`?  Resuming needs the `window` rows before snap_pos; the ring has
+    ring - window - block - 8 rows of slack beyond what one step reads, and rows older than that
+    have been overwritten (tokenrush/session.py:282-285: the prompt-end snapshot is dropped once
+    P - snap.pos exceeds that slack; ring size: tokenrush/dflash.py:139-146)."""
+    return cur_pos - snap_pos <= ring - window - block - 8
+
+
 class ShardedState(State):
     """One rank's shard of the KV state.  The last rank carries `headroom` extra rows so that
     the sequence can grow past the window."""
@@ -57,7 +90,15 @@ class ShardedState(State):
         lo, hi = shard_range(rank, world, window)
         rows = hi - lo + (headroom if rank == world - 1 else 0)
         super().__init__(cfg, rows, device, kv_dtype=kv_dtype, shard_lo=lo, pos_dtype=pos_dtype)
-        self.rank, self.world, self.window = rank, world, window
+        self.rank, self.world, self.window, self.headroom = rank, world, window, headroom
+
+    def resume_at(self, pos: int) -> dict:
+        """Resume (or rewind to) position `pos` on this rank: sets the replicated cursor and returns the
+        plan of `resume_plan`, plus this rank's own live rows.  Every rank makes the same call."""
+        plan = resume_plan(pos, self.world, self.window, self.headroom)
+        self.set_pos(pos)
+        plan["live_here"] = plan["live"][self.rank]
+        return plan
 
 
 class PartialExchange:
