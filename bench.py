@@ -627,7 +627,7 @@ def run_timeline(args):
     if not hasattr(lib, "trb_dbg_timeline"):
         raise SystemExit("the loaded library has no timeline: build it with `python -m tokenrush_b200.build --timeline`")
     lib.trb_dbg_timeline.argtypes, lib.trb_dbg_timeline.restype = [C.c_void_p, C.c_size_t], C.c_int
-    rows, m = args.rows or 32768, 1
+    rows, m = args.rows or 32768, args.m
     tb.fused.set_launch_mode(args.launch_mode)
     cfg = tb.AttnConfig(n_attn=LAYERS)
     st = tb.State(cfg, rows + 256, "cuda", kv_dtype=torch.float8_e4m3fn)
@@ -703,7 +703,7 @@ def run_timeline(args):
                 seg[nm] = round(float(np.median((a[sel, j2] - a[sel, i]) / 1e3)), 2)
         rec["per_cta_median_us"] = seg
         launches.append(rec)
-    print(json.dumps({"timeline": {"rows": rows, "layers": LAYERS, "launch_mode": args.launch_mode, "decode_only": bool(args.decode_only),
+    print(json.dumps({"timeline": {"rows": rows, "query_rows": m, "layers": LAYERS, "launch_mode": args.launch_mode, "decode_only": bool(args.decode_only),
                                    "us_per_step": round(us_step, 2), "us_per_layer": round(us_step / LAYERS, 2), "stamp_names": TL_NAMES,
                                    "launches": launches[-4:], "device_status": tb._lib.device_status()}}), flush=True)
 

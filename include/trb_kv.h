@@ -244,6 +244,20 @@ int trb_spec_commit(const int64_t *pred, const int64_t *drafts, int32_t k, int64
 /* pos <- pos + delta (State.advance, tokenrush/state.py:60-62), on the device. */
 int trb_cursor_advance(void *pos, int32_t pos_width, int64_t delta, trb_stream_t stream);
 
+/* ------------------------------------------------------------------ the step after attention
+ * Replaces fused.add_rmsnorm (tokenrush/fused.py:22-60), the consumer of the attention output once
+ * it has gone through the output projection (tokenrush/model.py:119-120).  The decode entry
+ * points write `out` as [m, hq*d] bf16 with the sigmoid gate applied, which is the row layout the
+ * projection's split-K GEMV reads; its result comes back as h:
+ *   h_splits  = 0: no h (x_out is not written: the residual is x itself);
+ *   h_splits  < 0: h [t_rows, n] bf16;
+ *   h_splits  > 0: h [h_splits, t_rows, n] fp32 partial rows, summed in split order and rounded to
+ *                  bf16 first (what a plain projection would have produced).
+ * x_out = bf16(x + h); y = RMSNorm(x_out) with the (1 + weight) gain, or, plain != 0, Qwen3's
+ * weight * bf16(normalised) form (the DFlash draft).  x, weight bf16; n a multiple of 8, <= 8192. */
+int trb_add_rmsnorm(const void *x, const void *h, int32_t h_splits, const void *weight, float eps, int32_t plain,
+                    int32_t t_rows, int32_t n, void *x_out, void *y, trb_stream_t stream);
+
 /* ------------------------------------------------------------------ chunked prefill
  * Replaces fused.attn_prefill_fused (tokenrush/fused.py:476-533): t queries q [t, hq, d] bf16 at
  * host position pos over cache rows 0..pos+t-1 (the chunk's own rows already appended in

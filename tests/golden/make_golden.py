@@ -40,7 +40,8 @@ def bf(bits):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference tree (the directory that holds tokenrush/)")
+    ap.add_argument("--only", default=None, help="write just this fixture (e.g. add_rmsnorm)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     from tokenrush import fused, ops                       # the reference
@@ -53,6 +54,22 @@ def main():
                       eps=1e-6, max_pos=4096, eos_ids=(0,))           # tests/test_ops.py:24-27
     HQ, HKV, D = 24, 4, 256
     f8 = torch.float8_e4m3fn
+
+    # ---- 0. residual add + RMSNorm, the torch chain the reference tests its add_rmsnorm kernel
+    # against (tests/test_fused.py:21-28,241-246,326-331): ops.rmsnorm / dflash.rmsnorm_plain over x + h
+    from tokenrush.dflash import rmsnorm_plain
+    xb_, hb_, wb_ = O.seeded_bf16(401, 3, 5120), O.seeded_bf16(402, 3, 5120, std=0.3), O.seeded_bf16(403, 5120, std=0.5)
+    x_, h_, w_ = bf(xb_), bf(hb_), bf(wb_)
+    parts = torch.Generator().manual_seed(404)
+    hp = torch.randn(4, 3, 5120, generator=parts) * 0.2                       # split-K partial rows, fp32
+    xs = (x_.float() + hp.sum(0).to(torch.bfloat16).float()).to(torch.bfloat16)
+    np.savez_compressed(os.path.join(HERE, "add_rmsnorm.npz"), x_bits=xb_, h_bits=hb_, w_bits=wb_, h_parts=hp.numpy(),
+                        xo_bits=O.torch_bf16_to_bits(x_ + h_), y_bits=O.torch_bf16_to_bits(ops.rmsnorm(x_ + h_, w_, 1e-6)),
+                        y_noh_bits=O.torch_bf16_to_bits(ops.rmsnorm(x_, w_, 1e-6)),
+                        y_plain_bits=O.torch_bf16_to_bits(rmsnorm_plain(x_ + h_, w_ + 1, 1e-6)),
+                        xo_parts_bits=O.torch_bf16_to_bits(xs), y_parts_bits=O.torch_bf16_to_bits(ops.rmsnorm(xs, w_, 1e-6)))
+    if args.only == "add_rmsnorm":
+        return
 
     # ---- 1. FP8 append: random rows + edge rows ------------------------------------------
     T = 40

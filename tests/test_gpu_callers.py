@@ -153,3 +153,36 @@ def test_ops_callables_over_bf16_cache(tb):
     pos_t = torch.tensor([pos + i], device="cuda")
     o2 = tb.ops.attn_decode_bucket(q[:, i:i + 1], st.k[0, :, :128], st.v[0, :, :128], pos_t)
     assert torch.equal(o1, o2)
+
+
+def test_add_rmsnorm_after_the_output_projection(tb, golden_dir):
+    """The step after attention: the decode output is [M, HQ*D] bf16, the rows the output projection
+    reads; its (split-K) result goes through add_rmsnorm.  Against the reference's golden vectors:
+    the residual sum bit for bit, the normed rows within one bf16 step (the fp32 mean of squares is
+    summed in another order than torch's CPU reduction) and mostly bit for bit."""
+    z = np.load(os.path.join(golden_dir, "add_rmsnorm.npz"))
+    x, h, w = to_dev(z["x_bits"]), to_dev(z["h_bits"]), to_dev(z["w_bits"])
+
+    def close(got_bits, want_bits, what):
+        g, wv = O.bf16_bits_to_f32(got_bits), O.bf16_bits_to_f32(want_bits)
+        assert (np.abs(g - wv) <= 2.0 ** -7 * np.abs(wv) + 1e-6).all(), what
+        assert (got_bits == want_bits).mean() > 0.99, (what, float((got_bits == want_bits).mean()))
+    xo, y = tb.fused.add_rmsnorm(x, h, w, 1e-6)
+    assert np.array_equal(bits_of(xo), z["xo_bits"])
+    close(bits_of(y), z["y_bits"], "bf16 h")
+    xo, y = tb.fused.add_rmsnorm(x, None, w, 1e-6)
+    assert xo is x
+    close(bits_of(y), z["y_noh_bits"], "no h")
+    xo, y = tb.fused.add_rmsnorm(x, h, (w.float() + 1).to(torch.bfloat16), 1e-6, plain=True)
+    close(bits_of(y), z["y_plain_bits"], "plain gain")
+    xo, y = tb.fused.add_rmsnorm(x, torch.from_numpy(z["h_parts"]).cuda(), w, 1e-6)
+    assert np.array_equal(bits_of(xo), z["xo_parts_bits"])                       # split partials summed in split order
+    close(bits_of(y), z["y_parts_bits"], "fp32 partials")
+    # hand-off: what attn_decode_fused returns is what a projection over [M, HQ*D] rows takes as it is
+    cfg = tb.AttnConfig(n_attn=1)
+    st = tb.State(cfg, 128, "cuda", kv_dtype=torch.float8_e4m3fn)
+    st.set_pos(7)
+    o = tb.fused.attn_decode_fused(torch.zeros(2, HQ * D, device="cuda", dtype=torch.bfloat16), None, st.k[0], st.v[0], st.pos_t, cfg,
+                                   st.k_scale[0], st.v_scale[0])
+    assert o.shape == (2, HQ * D) and o.is_contiguous() and o.dtype == torch.bfloat16
+    assert tb._lib.device_status() == 0

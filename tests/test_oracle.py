@@ -171,3 +171,19 @@ def test_attention_edge_lengths(L):
     if L == 0:      # one visible key: the output is that key's dequantised V row
         _, vd = st.dequant(0, 1)
         np.testing.assert_allclose(o[0].reshape(HKV, 6, D), np.repeat(vd[:, 0][:, None], 6, axis=1), atol=1e-6)
+
+
+def test_add_rmsnorm_matches_reference_golden(golden_dir):
+    """The residual add + RMSNorm chain (the step after the attention output projection) against what
+    the reference's torch functions returned: every bf16 bit."""
+    z = np.load(os.path.join(golden_dir, "add_rmsnorm.npz"))
+    B = O.bits_to_torch_bf16
+    x, h, w = B(z["x_bits"]), B(z["h_bits"]), B(z["w_bits"])
+    xo, y = O.add_rmsnorm(x, h, w, 1e-6)
+    assert np.array_equal(O.torch_bf16_to_bits(xo), z["xo_bits"]) and np.array_equal(O.torch_bf16_to_bits(y), z["y_bits"])
+    xo, y = O.add_rmsnorm(x, None, w, 1e-6)
+    assert xo is x and np.array_equal(O.torch_bf16_to_bits(y), z["y_noh_bits"])
+    xo, y = O.add_rmsnorm(x, h, w + 1, 1e-6, plain=True)
+    assert np.array_equal(O.torch_bf16_to_bits(y), z["y_plain_bits"])
+    xo, y = O.add_rmsnorm(x, torch.from_numpy(z["h_parts"]), w, 1e-6)
+    assert np.array_equal(O.torch_bf16_to_bits(xo), z["xo_parts_bits"]) and np.array_equal(O.torch_bf16_to_bits(y), z["y_parts_bits"])

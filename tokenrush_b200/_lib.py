@@ -73,6 +73,8 @@ SIGNATURES = {
     "trb_spec_commit": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
                                   C.c_void_p]),
     "trb_cursor_advance": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_void_p]),
+    "trb_add_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_float, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                  C.c_void_p, C.c_void_p]),
     "trb_attn_prefill": (C.c_int, [C.POINTER(Cache), C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_float,
                                    C.c_void_p]),
     "trb_p2p_create": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_void_p]),

@@ -42,6 +42,7 @@ __device__ __forceinline__ unsigned long long tl_now() {
     return t;
 }
 #define TRB_TL(buf, slot) do { if (threadIdx.x == 0) (buf)[slot] = tl_now(); } while (0)
+#define TRB_TL_IF(cond, buf, slot) do { if (cond) (buf)[slot] = tl_now(); } while (0)
 #define TRB_TL_SET(buf, slot, v) do { if (threadIdx.x == 0) (buf)[slot] = (unsigned long long)(v); } while (0)
 #define TRB_TL_FLUSH(buf, launch, cta)                                                                   \
     do {                                                                                                  \
@@ -52,6 +53,7 @@ __device__ __forceinline__ unsigned long long tl_now() {
     } while (0)
 #else
 #define TRB_TL(buf, slot) do { } while (0)
+#define TRB_TL_IF(cond, buf, slot) do { } while (0)
 #define TRB_TL_SET(buf, slot, v) do { } while (0)
 #define TRB_TL_FLUSH(buf, launch, cta) do { } while (0)
 #endif

@@ -62,6 +62,8 @@ struct DecodeParams {
     Cursor pos;
     long long max_len, ring, shard_lo;
     int sharded;
+    int tail_rows_per_helper;     // output rows merged by one helper CTA (several when its shared memory holds two rows' partials)
+    int tail_teams;               // the launch ends with decode_tail_teams (tensor-core kernel)
     int pdl_flags;                // PDL_*: what this launch may touch before its dependency wait
     // rows pos .. pos + m - 1 taken from the source rows of the append that is still writing them
     // (fresh_k == nullptr: they are read from the cache like every other row)
@@ -136,12 +138,19 @@ __device__ __forceinline__ void decode_ticket(const DecodeParams &p, const int j
     if (arrival == (unsigned int)(active - 1)) atomicAdd(p.word + j, (1ull << 16) - (unsigned long long)active);
     // More arrivals than splits: the word was not zeroed, or two launches overlap on one workspace.
     if (arrival >= (unsigned int)active) raise_status(TRB_ST_WORKSPACE);
-    const int rc = (p.rows > active && p.p2p_world == 0 && groups >= 2) ? 2 : 1;     // rows per claim
-    const int nclaims = (p.rows + rc - 1) / rc;
-    const int helpers = nclaims < active ? nclaims : active;
-    // the rows are merged by the last CTAs of this kv head to arrive, one claim (one or two rows) at a
-    // time: arrival number a makes a CTA helper a - (active - helpers); earlier arrivals leave after
-    // writing their partial and free their SM for the next kernel in the stream
+    // The rows are merged by the last CTAs of this kv head to arrive, a helper taking every
+    // helpers-th row: arrival number a makes a CTA helper a - (active - helpers); earlier arrivals
+    // leave after writing their partial and free their SM for the next kernel in the stream.  Few
+    // helpers, several rows each: the helpers are the CTAs that wait (for the slowest partial, and
+    // for the launches before this one), so the fewer they are the fewer SMs stand still.
+    int want;
+    if (p.tail_teams) {                                       // decode_tail_teams: claims of two rows when there are more rows than splits
+        const int rc = (p.rows > active && p.p2p_world == 0 && groups >= 2) ? 2 : 1;
+        want = (p.rows + rc - 1) / rc;
+    } else {
+        want = (p.rows + p.tail_rows_per_helper - 1) / p.tail_rows_per_helper;
+    }
+    const int helpers = want < active ? want : active;
     const int h = (int)arrival - (active - helpers);
     sm_flag[0] = (h >= 0 && h < helpers) ? h : -1;
     sm_flag[2] = (int)(unsigned int)(old >> 16);
@@ -165,12 +174,366 @@ __device__ __forceinline__ bool poll_tagged(const uint4 *src, const unsigned int
     return v.y == tag && v.w == tag;
 }
 
+// Bulk copy global -> shared (size a multiple of 16 bytes, both addresses 16-byte aligned);
+// completes on the mbarrier with its byte count.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // Tail: LSE merge of the output rows over the active splits (+ extra partials), in split order,
+// by the helper CTAs.  Called by every thread of the CTA after the CTA's own partial rows are
+// on their way to the workspace and sm_flag is visible.  `smem` .. `smem + smem_bytes` is scratch
+// once every thread has passed the first barrier below.
+//
+// A row's partials (one per active split: 2 KB at D = 256, plus the (max, sum) entries) are fetched
+// into shared memory with bulk copies, all in flight at once on one mbarrier: one round trip for
+// the whole row and no registers tied up.  The tags of what arrived are then checked; splits
+// whose partial had not been written yet are fetched again (bounded), and only then the row is
+// merged, in split order, from shared memory.  With room for two rows the next row's copies are
+// in flight while this one is merged.
+template <int D, int NTHREADS>
+__device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem, const int smem_bytes, const int *sm_flag, const int j,
+                                            const int active, unsigned long long *tl = nullptr) {
+    (void)tl;
+    const int helper = sm_flag[0];
+    if (helper < 0) return;
+    TRB_TL(tl, 9);
+    const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
+    const int tid = threadIdx.x, lane = threadIdx.x & 31;
+    constexpr int ITEMS = D / 4, GROUPS = NTHREADS / ITEMS;
+    const int want = (p.rows + p.tail_rows_per_helper - 1) / p.tail_rows_per_helper;       // as in decode_ticket
+    const int helpers = want < active ? want : active;
+    const int max_rounds = (int)(c_wait_limit[1] >> 8) + 4;            // fetch rounds before a row gives up
+
+    // Thread (item, group) sums the splits of its group, the groups are added in group order
+    // through shared memory.
+    const int n_parts = active + p.n_extra;
+    const int item = tid % ITEMS, tgrp = tid / ITEMS, d4 = item * 4;
+    const bool in_team = tgrp < GROUPS;                                 // (threads beyond the last whole group idle)
+    constexpr int gt = GROUPS;
+    // ---- shared memory of the tail
+    float *sm_m = reinterpret_cast<float *>(smem);                      // [n_parts]
+    float *sm_l = sm_m + (DEC_MAX_SPLITS + 4);                          // [n_parts]
+    constexpr int RED_OFF = 2 * (DEC_MAX_SPLITS + 4) * 4;
+    float4 *sm_red = reinterpret_cast<float4 *>(smem + RED_OFF);        // [GROUPS][ITEMS]
+    constexpr int BAR_OFF = RED_OFF + GROUPS * ITEMS * 16;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(smem + BAR_OFF);       // [2]
+    uint8_t *sm_bad_all = smem + BAR_OFF + 16;                          // [2][DEC_MAX_SPLITS + 4] split's partial not here yet
+    constexpr int BAD_STRIDE = DEC_MAX_SPLITS + 4;
+    constexpr int FRESH_OFF = (BAR_OFF + 16 + 2 * BAD_STRIDE + 127) / 128 * 128;
+    const int n_fresh = p.fresh_k ? p.m : 0;
+    float *fr_k = reinterpret_cast<float *>(smem + FRESH_OFF);          // [n_fresh][D]
+    float *fr_v = fr_k + n_fresh * D;                                   // [n_fresh][D]
+    float *fr_s = fr_v + n_fresh * D;                                   // [8] scores of the current row, log2 units
+    int *fr_held = reinterpret_cast<int *>(fr_s + 8);                   // [8] this cache holds the row's position
+    const int bulk_off = (FRESH_OFF + 2 * n_fresh * D * 4 + 64 + 127) / 128 * 128;
+    const int ml_bytes = (active * 16 + 127) / 128 * 128;
+    const int buf_bytes = ml_bytes + active * D * 8;                    // one row: (max, sum) entries, then the accumulators
+    const int nbuf = (smem_bytes - bulk_off >= 2 * buf_bytes) ? 2 : 1;  // (the host sized the splits so that one row always fits)
+    bool all_ok = true;
+    uint32_t phase[2] = {0u, 0u};
+
+    // ---- the m rows that the append of this step is still writing, from its source rows: quantised
+    // and dequantised exactly as the append does (tokenrush/fused.py:336-340), kept as fp32 rows of
+    // this kv head in shared memory.  They enter the merge below as one more partial.
+    constexpr int EPL = D / 32;
+    const int fr_row = tid >> 5;                                        // the fresh row this warp prepares (rows beyond the warp count: below)
+    __nv_bfloat16 fr_raw[2][EPL];
+    if (fr_row < n_fresh) {                                             // requested now, used once the partial copies are out
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+            const __nv_bfloat16 *src = (which ? p.fresh_v : p.fresh_k) + (long long)j * p.fresh_hs + (long long)fr_row * p.fresh_rs + lane * EPL;
+            if (EPL == 8) *reinterpret_cast<uint4 *>(fr_raw[which]) = *reinterpret_cast<const uint4 *>(src);
+            else *reinterpret_cast<uint2 *>(fr_raw[which]) = *reinterpret_cast<const uint2 *>(src);
+        }
+    }
+    // quantise + dequantise one source row held as EPL values per lane, into shared memory
+    auto fresh_store = [&](int r, int which, const __nv_bfloat16 (&raw)[EPL]) {
+        float f[EPL];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) f[e] = __bfloat162float(raw[e]);
+        if (p.ks) {
+            float amax = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) amax = fmaxf(amax, fabsf(f[e]));
+            amax = warp_max(amax);
+            const float sc = __fdiv_rn(fmaxf(amax, 1e-6f), 448.0f);
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                const __nv_fp8_storage_t code = __nv_cvt_float_to_fp8(__fdiv_rn(f[e], sc), __NV_SATFINITE, __NV_E4M3);
+                f[e] = __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3))) * sc;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) (which ? fr_v : fr_k)[r * D + lane * EPL + e] = f[e];
+    };
+
+    __syncthreads();                                                    // the CTA's own partial has left shared memory: it is scratch now
+    if (tid == 0) { mbar_init(&bar[0], 1u); mbar_init(&bar[1], 1u); mbar_fence_init(); }
+    for (int i = tid; i < 2 * BAD_STRIDE; i += NTHREADS) sm_bad_all[i] = 1;   // nothing fetched yet
+    __syncthreads();
+
+    const long long ws_row0 = (long long)j * p.nsplit * p.rows_pad;     // first workspace row of this kv head
+    // warp 0: request every split of `row` that is marked missing into buffer b (all copies on one barrier)
+    auto fetch = [&](int row, int b) {
+        if (tid < 32) {
+            uint8_t *bad = sm_bad_all + b * BAD_STRIDE;
+            uint8_t *buf = smem + bulk_off + b * buf_bytes;
+            uint32_t bytes = 0;
+            for (int sp = lane; sp < active; sp += 32)
+                if (bad[sp]) bytes += D * 8 + 16;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) bytes += __shfl_xor_sync(0xffffffffu, bytes, off);
+            if (lane == 0) { fence_proxy_async_smem(); mbar_arrive_expect_tx(&bar[b], bytes); }
+            __syncwarp();
+            for (int sp = lane; sp < active; sp += 32)
+                if (bad[sp]) {
+                    const long long wrow = ws_row0 + (long long)sp * p.rows_pad + row;
+                    bulk_g2s(buf + ml_bytes + (size_t)sp * D * 8, p.part_acc + wrow * D, D * 8, &bar[b]);
+                    bulk_g2s(buf + sp * 16, p.part_ml + wrow, 16, &bar[b]);
+                }
+        }
+    };
+    int nk = 0;
+    for (int row = helper; row < p.rows; row += helpers) ++nk;
+    if (nk > 0) fetch(helper, 0);
+    if (n_fresh) {                                                      // the fresh rows of this kv head into shared memory
+        const long long pos = load_cursor(p.pos);
+        for (int r = fr_row; r < n_fresh; r += NTHREADS / 32) {
+            if (r != fr_row) {                                          // more fresh rows than warps: fetched here
+#pragma unroll
+                for (int which = 0; which < 2; ++which) {
+                    const __nv_bfloat16 *src = (which ? p.fresh_v : p.fresh_k) + (long long)j * p.fresh_hs + (long long)r * p.fresh_rs + lane * EPL;
+                    if (EPL == 8) *reinterpret_cast<uint4 *>(fr_raw[which]) = *reinterpret_cast<const uint4 *>(src);
+                    else *reinterpret_cast<uint2 *>(fr_raw[which]) = *reinterpret_cast<const uint2 *>(src);
+                }
+            }
+            fresh_store(r, 0, fr_raw[0]);
+            fresh_store(r, 1, fr_raw[1]);
+            const long long loc = pos + r - p.shard_lo;                 // a sequence shard holds a range of positions
+            if (lane == 0) fr_held[r] = (loc >= 0 && loc < p.max_len) ? 1 : 0;
+        }
+    }
+    for (int k = 0; k < nk; ++k) {
+        const int row = helper + k * helpers, b = nbuf == 2 ? (k & 1) : 0;
+        const bool row_on = in_team;
+        const int qi = row / p.g, hq = j * p.g + row % p.g;
+        const long long grow = (long long)qi * p.hq + hq;
+        uint8_t *bad = sm_bad_all + b * BAD_STRIDE;
+        const uint4 *bk_ml = reinterpret_cast<const uint4 *>(smem + bulk_off + b * buf_bytes);
+        const uint4 *bk_acc = reinterpret_cast<const uint4 *>(smem + bulk_off + b * buf_bytes + ml_bytes);
+        if (nbuf == 2 && k + 1 < nk) fetch(row + helpers, b ^ 1);      // the next row's copies fly while this row is merged
+        // ---- fetch rounds of this row
+        for (int round = 0;; ++round) {
+            const bool landed = mbar_wait(&bar[b], phase[b]);
+            phase[b] ^= 1u;
+            __syncthreads();                                            // warp 0 has read the old marks
+            for (int i = tid; i < BAD_STRIDE; i += NTHREADS) bad[i] = 0;
+            __syncthreads();
+            // check the tags of everything this thread will use
+            bool miss = !landed;
+            if (in_team)
+                for (int sp = tgrp; sp < active; sp += gt) {
+                    const uint4 a0 = bk_acc[(size_t)sp * (D / 2) + item * 2], a1 = bk_acc[(size_t)sp * (D / 2) + item * 2 + 1];
+                    if (!(a0.y == tag && a0.w == tag && a1.y == tag && a1.w == tag)) { bad[sp] = 1; miss = true; }
+                }
+            for (int sp = tid; sp < active; sp += NTHREADS) {
+                const uint4 w = bk_ml[sp];
+                if (!(w.y == tag && w.w == tag)) { bad[sp] = 1; miss = true; }
+            }
+            if (!__syncthreads_or(miss ? 1 : 0)) break;                 // the whole row is here
+            // give up after the limit (or soon, once a wait of this process has run out: a stale workspace
+            // costs one limit, not one per row); one thread decides for all
+            const bool stop = tid == 0 && (round >= max_rounds || (round >= 8 && (*(volatile unsigned int *)&g_status & TRB_ST_WAIT_TIMEOUT)));
+            if (__syncthreads_or(stop ? 1 : 0)) {
+                all_ok = false;                                         // the missing splits count as empty
+                break;
+            }
+            __nanosleep(round < 4 ? 100 : 500);
+            fetch(row, b);
+        }
+        // ---- (max, sum) of all splits, the scores of the fresh keys, the weights' reference
+        for (int sp = tid; sp < n_parts; sp += NTHREADS) {
+            float2 v;
+            if (sp < active) {
+                const uint4 w = bk_ml[sp];
+                v = (w.y == tag && w.w == tag) ? make_float2(__uint_as_float(w.x), __uint_as_float(w.z)) : make_float2(-INFINITY, 0.f);
+            } else {
+                v = *reinterpret_cast<const float2 *>(&p.extra_ml[(grow * p.n_extra + (sp - active)) * 2]);
+            }
+            sm_m[sp] = v.x; sm_l[sp] = v.y;
+        }
+        if (n_fresh) {                                                  // one warp per fresh key
+            const __nv_bfloat16 *qp = p.q + grow * D + lane * EPL;
+            for (int r = tid >> 5; r < n_fresh; r += NTHREADS / 32) {
+                float dot = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) dot = fmaf(__bfloat162float(qp[e]), fr_k[r * D + lane * EPL + e], dot);
+                dot = warp_sum(dot);
+                if (lane == 0) fr_s[r] = dot * p.scale_log2;
+            }
+        }
+        __syncthreads();
+        TRB_TL(tl, 10);
+        float mmax = -INFINITY, lsum = 0.f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row_on) {
+            for (int sp = lane; sp < n_parts; sp += 32) mmax = fmaxf(mmax, sm_m[sp]);
+            mmax = warp_max(mmax);
+            // fresh keys 0..qi are visible to query row qi (tokenrush/fused.py:382: keys <= pos + qi)
+            const int n_vis = n_fresh ? (qi + 1 < n_fresh ? qi + 1 : n_fresh) : 0;
+            for (int r = 0; r < n_vis; ++r)
+                if (fr_held[r]) mmax = fmaxf(mmax, fr_s[r]);
+            for (int sp = lane; sp < n_parts; sp += 32) lsum += sm_m[sp] == -INFINITY ? 0.f : fast_exp2(sm_m[sp] - mmax) * sm_l[sp];
+            lsum = warp_sum(lsum);
+            for (int r = 0; r < n_vis; ++r)
+                if (fr_held[r]) {
+                    const float w = fast_exp2(fr_s[r] - mmax);
+                    lsum += w;
+                    if (tgrp == 0) {
+                        const float4 v = *reinterpret_cast<const float4 *>(&fr_v[r * D + d4]);
+                        o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+                    }
+                }
+            // the accumulators, split order within the group: ascending
+            for (int sp = tgrp; sp < active; sp += gt) {
+                const uint4 a0 = bk_acc[(size_t)sp * (D / 2) + item * 2], a1 = bk_acc[(size_t)sp * (D / 2) + item * 2 + 1];
+                const bool here = a0.y == tag && a0.w == tag && a1.y == tag && a1.w == tag;
+                const float w = (sm_m[sp] == -INFINITY || !here) ? 0.f : fast_exp2(sm_m[sp] - mmax);
+                o.x = fmaf(w, __uint_as_float(a0.x), o.x); o.y = fmaf(w, __uint_as_float(a0.z), o.y);
+                o.z = fmaf(w, __uint_as_float(a1.x), o.z); o.w = fmaf(w, __uint_as_float(a1.z), o.w);
+            }
+            if (tgrp == 0)
+                for (int e = 0; e < p.n_extra; ++e) {
+                    const float4 v = *reinterpret_cast<const float4 *>(&p.extra_acc[(grow * p.n_extra + e) * D + d4]);
+                    const float w = sm_m[active + e] == -INFINITY ? 0.f : fast_exp2(sm_m[active + e] - mmax);
+                    o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+                }
+            sm_red[tgrp * ITEMS + item] = o;
+        }
+        for (int i = tid; i < BAD_STRIDE; i += NTHREADS) bad[i] = 1;   // the buffer's next row: nothing fetched yet
+        __syncthreads();                                                // ... and the buffer may be refilled
+        TRB_TL(tl, 11);
+        if (nbuf == 1 && k + 1 < nk) fetch(row + helpers, 0);
+        const bool lead = row_on && tgrp == 0;                           // these threads hold the row from here on
+        if (lead) {
+            for (int kk = 1; kk < gt; ++kk) {
+                const float4 v = sm_red[kk * ITEMS + item];
+                o.x += v.x; o.y += v.y; o.z += v.z; o.w += v.w;
+            }
+        }
+        // Outputs (and the exchange with other GPUs) only once every earlier launch is complete.  The
+        // helpers are the CTAs of a launch that always wait, so a launch never completes before
+        // the launches it follows; with a private workspace the other CTAs have left without waiting.
+        pdl_wait();
+        if (p.shard_acc) {
+            if (lead) {
+                *reinterpret_cast<float4 *>(&p.shard_acc[grow * D + d4]) = o;
+                if (item == 0) { p.shard_ml[grow * 2] = mmax; p.shard_ml[grow * 2 + 1] = lsum; }
+            }
+            continue;
+        }
+        if (p.p2p_world > 1 && lead) {
+            // ---- sequence shards: exchange this row's (max, sum, acc) with the other GPUs by peer
+            // stores, wait (bounded) for theirs, merge in rank order.  Every 8 bytes that cross the
+            // link are (value, tag): the receiver polls the data itself, so there is no flag, no fence
+            // and no second message.  The tag is this kv head's launch epoch + 1, identical on all GPUs
+            // because they make the same calls on their workspaces; slots rotate over P2P_SLOTS calls
+            // (a GPU cannot be more than one call ahead of a peer whose packets it waits for).  This
+            // GPU's own partial stays in registers.
+            const P2PLayout xl = p2p_layout(p.p2p_world, p.m * p.hq, D);
+            const size_t slot = tag % P2P_SLOTS;
+            const size_t nrow = (size_t)(p.m * p.hq);
+            const uint4 k0 = make_uint4(__float_as_uint(o.x), tag, __float_as_uint(o.y), tag);
+            const uint4 k1 = make_uint4(__float_as_uint(o.z), tag, __float_as_uint(o.w), tag);
+            const uint4 k2 = make_uint4(__float_as_uint(mmax), tag, __float_as_uint(lsum), tag);
+            for (int r = 0; r < p.p2p_world; ++r) {
+                if (r == p.p2p_rank) continue;
+                uint4 *dst = reinterpret_cast<uint4 *>((uint8_t *)p.p2p_ptr[r] + xl.ll) +
+                             (((slot * p.p2p_world + p.p2p_rank) * nrow + grow) * ITEMS + item) * 3;
+                st_volatile_v4(dst, k0); st_volatile_v4(dst + 1, k1); st_volatile_v4(dst + 2, k2);
+            }
+            const uint4 *local = reinterpret_cast<const uint4 *>((const uint8_t *)p.p2p_ptr[p.p2p_rank] + xl.ll);
+            // one polling loop over all peers: a peer's three packets are taken when all six tags match
+            const unsigned int plimit = c_wait_limit[2];
+            uint4 pk[P2P_MAX_WORLD][3];
+            unsigned int pending = 0u;
+            for (int r = 0; r < p.p2p_world; ++r)
+                if (r != p.p2p_rank) pending |= 1u << r;
+            for (unsigned int it = 0; it < plimit && pending; ++it) {
+#pragma unroll
+                for (int r = 0; r < P2P_MAX_WORLD; ++r) {
+                    if (!((pending >> r) & 1u)) continue;
+                    const uint4 *src = local + (((slot * p.p2p_world + r) * nrow + grow) * ITEMS + item) * 3;
+                    const uint4 b0 = ld_volatile_v4(src), b1 = ld_volatile_v4(src + 1), b2 = ld_volatile_v4(src + 2);
+                    if (b0.y == tag && b0.w == tag && b1.y == tag && b1.w == tag && b2.y == tag && b2.w == tag) {
+                        pk[r][0] = b0; pk[r][1] = b1; pk[r][2] = b2;
+                        pending &= ~(1u << r);
+                    }
+                }
+                if (it > 64) __nanosleep(100);
+                // once a wait of this process has run out, later ones give up early: a lost peer costs
+                // one limit, not one limit per row and layer
+                if (it == 4096 && (*(volatile unsigned int *)&g_status & TRB_ST_PEER_TIMEOUT)) break;
+            }
+            if (pending) {
+                raise_status(TRB_ST_PEER_TIMEOUT);
+            } else {
+                float gm = mmax;
+#pragma unroll
+                for (int r = 0; r < P2P_MAX_WORLD; ++r)
+                    if (r < p.p2p_world && r != p.p2p_rank) gm = fmaxf(gm, __uint_as_float(pk[r][2].x));
+                // weights and sums in rank order, own partial from registers
+                float gl = 0.f;
+                float4 go = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int r = 0; r < P2P_MAX_WORLD; ++r) {
+                    if (r >= p.p2p_world) continue;
+                    float2 mlr = make_float2(mmax, lsum);
+                    float4 v = o;
+                    if (r != p.p2p_rank) {
+                        v = make_float4(__uint_as_float(pk[r][0].x), __uint_as_float(pk[r][0].z), __uint_as_float(pk[r][1].x), __uint_as_float(pk[r][1].z));
+                        mlr = make_float2(__uint_as_float(pk[r][2].x), __uint_as_float(pk[r][2].z));
+                    }
+                    const float w = mlr.x == -INFINITY ? 0.f : fast_exp2(mlr.x - gm);
+                    gl = fmaf(w, mlr.y, gl);
+                    go.x = fmaf(w, v.x, go.x); go.y = fmaf(w, v.y, go.y); go.z = fmaf(w, v.z, go.z); go.w = fmaf(w, v.w, go.w);
+                }
+                o = go; lsum = gl;
+            }
+        }
+        if (!lead) continue;
+        const float inv = 1.f / lsum;
+        float r[4] = {o.x * inv, o.y * inv, o.z * inv, o.w * inv};
+        __nv_bfloat16 ob[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ob[e] = __float2bfloat16_rn(r[e]);
+        if (p.gate) {
+            const __nv_bfloat16 *gp = p.gate + (long long)qi * p.gate_rs + (long long)hq * p.gate_hs + d4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float gv = __bfloat162float(gp[e]);
+                const float sg = __bfloat162float(__float2bfloat16_rn(1.f / (1.f + __expf(-gv))));
+                ob[e] = __float2bfloat16_rn(__bfloat162float(ob[e]) * sg);
+            }
+        }
+        *reinterpret_cast<uint2 *>(&p.out[grow * D + d4]) = *reinterpret_cast<const uint2 *>(ob);
+    }
+    if (!all_ok) raise_status(TRB_ST_WAIT_TIMEOUT);
+}
+
+// The tail of the tensor-core kernel (M-row verify): the same merge as decode_tail, with the
+// partials loaded straight into registers and two rows per claim.  That kernel fills an SM alone and
+// all its CTAs finish together, so many helpers with one short claim each (one round trip) cost less
+// SM time than few helpers that fetch row after row.
+// LSE merge of the output rows over the active splits (+ extra partials), in split order,
 // by the helper CTAs.  Called by every thread of the CTA after the CTA's own partial rows are
 // on their way to the workspace and sm_flag is visible.  `smem` is scratch from its start (at
 // least 16 KB) once every thread has passed the barrier below.
 template <int D, int NTHREADS>
-__device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem, const int *sm_flag, const int j, const int active,
+__device__ __forceinline__ void decode_tail_teams(const DecodeParams &p, uint8_t *smem, const int *sm_flag, const int j, const int active,
                                             unsigned long long *tl = nullptr) {
     (void)tl;
     const int helper = sm_flag[0];
@@ -504,6 +867,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     int my_tiles = (t0 + per < n_tiles ? t0 + per : n_tiles) - t0;
     if (my_tiles < 0) my_tiles = 0;
 
+    // With a workspace of its own the CTA takes its ticket now: the order of STARTING then decides
+    // who merges the output rows.  All CTAs do the same work, so the last to start are the last to
+    // finish, and a helper finds (nearly) all partials written when it gets to them - it never sits
+    // on its SM waiting for CTAs that have not even been scheduled yet.
+    unsigned long long ticket = 0ull;
+    if (threadIdx.x == 0 && (flags & PDL_PRIVATE_WS)) ticket = decode_ticket_take(p, j);
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::NSTAGE; ++s) {
             mbar_init(&bar_full[s], FP8 ? 33u : 1u);
@@ -859,8 +1228,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     const bool ws_private = (flags & PDL_PRIVATE_WS) != 0;
     if (!ws_private) dep_wait();
     TRB_TL(sm_tl, 6);
-    unsigned long long ticket = 0ull;
-    if (threadIdx.x == 0) ticket = decode_ticket_take(p, j);
+    if (threadIdx.x == 0 && !ws_private) ticket = decode_ticket_take(p, j);
     // 1. merge the warps that share an 8-row slice (fixed order) through shared memory: every warp
     // stages its accumulators unscaled, together with its (max, sum); the reducing threads weigh them
     __syncthreads();                    // every stage has been consumed
@@ -907,7 +1275,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ 
     TRB_TL(sm_tl, 8);
     TRB_TL_SET(sm_tl, 13, sm_flag[0]);
     TRB_TL_SET(sm_tl, 14, my_tiles);
-    decode_tail<D, DEC_CTHREADS>(p, smem, sm_flag, j, active, sm_tl);
+    decode_tail<D, DEC_CTHREADS>(p, smem, C::SCALE_OFF, sm_flag, j, active, sm_tl);
     TRB_TL_FLUSH(sm_tl, (unsigned int)sm_flag[2], j * p.nsplit + split);
 }
 
@@ -996,10 +1364,20 @@ static int sm_count() {
     return g_sm_count;
 }
 
-// splits per kv head: one CTA per SM over all heads
-static int decode_nsplit(int hkv) {
+// Shared memory that the tail of the smallest kernel variant has for a row's partials, and the
+// bytes of its bookkeeping before them (see decode_tail): upper bounds, used to size the splits.
+constexpr int DEC_TAIL_SMEM_MIN = DEC_HALF_WARPS * DEC_STAGE_BYTES_PER_WARP;
+static int tail_bookkeeping_bytes(int d, int m) { return 9216 + 2 * m * d * 4 + 256; }
+
+// splits per kv head: one CTA per SM over all heads, and no more than a helper's shared memory
+// can hold of one row's partials (which only matters with one or two kv heads)
+static int decode_nsplit(int hq, int hkv, int d, int m) {
     int n = sm_count() / hkv;
     if (n > DEC_MAX_SPLITS) n = DEC_MAX_SPLITS;
+    // (the half-size CTA only serves one 8-row slice; every other variant has twice its shared memory or more)
+    const int tail_smem = (hq / hkv) * m <= 8 ? DEC_TAIL_SMEM_MIN : 2 * DEC_TAIL_SMEM_MIN;
+    const int fit = (tail_smem - tail_bookkeeping_bytes(d, m)) / (d * 8 + 16);
+    if (n > fit) n = fit;
     return n < 1 ? 1 : n;
 }
 
@@ -1096,7 +1474,7 @@ extern "C" size_t trb_decode_workspace_bytes(int32_t hq, int32_t hkv, int32_t d,
     const int rows = (hq / hkv) * m;
     if (rows > DEC_MAX_ROWS) return 0;
     const int rows_pad = (rows + 7) / 8 * 8;
-    return workspace_layout(hkv, decode_nsplit(hkv), rows_pad, d).total;
+    return workspace_layout(hkv, decode_nsplit(hq, hkv, d, m), rows_pad, d).total;
 }
 
 extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t *a, trb_stream_t stream) {
@@ -1126,7 +1504,7 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     p.ks = c.k_scale; p.vs = c.v_scale;
     p.m = a->m; p.hq = a->hq; p.hkv = c.hkv; p.g = g; p.rows = rows;
     p.nt = (rows + 7) / 8; p.kw = 0;                              // kw: set once the launch plan is known
-    p.nsplit = decode_nsplit(c.hkv); p.rows_pad = p.nt * 8;
+    p.nsplit = decode_nsplit(a->hq, c.hkv, c.d, a->m); p.rows_pad = p.nt * 8;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.new_rows = a->new_rows ? 1 : 0; p.window = a->window; p.n_extra = a->n_extra;
     p.extra_ml = a->extra_ml; p.extra_acc = a->extra_acc;
@@ -1169,7 +1547,17 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     // a ring cache maps several positions to one row: the rows below the cursor are not the rows
     // below the in-flight append
     if (c.ring > 0 && !(p.pdl_flags & PDL_ALL_STABLE)) p.pdl_flags &= (PDL_TRIGGER_TOP | PDL_PRIVATE_WS);
+    // The tensor-core kernel fills an SM alone: CTAs that ran ahead of the launch before would start
+    // and finish far apart, and its helpers would sit on their SMs waiting for the stragglers.  Its
+    // CTAs therefore all wait before the epilogue and finish together.
+    if (tensor_kernel || p.nt != 1) p.pdl_flags &= ~PDL_PRIVATE_WS;   // (likewise the full-size CTAs of the several-slice kernel)
+    p.tail_teams = tensor_kernel ? 1 : 0;
     p.kw = decode_warps(p) / (p.nt * (2 / decode_groups_per_warp(p.nt)));
+    {   // a helper merges several rows when its tail can hold two rows' partials (the next row's copies fly during a merge)
+        const int tail_smem = tensor_kernel ? TC_OFF_SC : decode_warps(p) * DEC_STAGE_BYTES_PER_WARP;
+        const int row_bytes_tail = (p.nsplit * 16 + 127) / 128 * 128 + p.nsplit * c.d * 8;
+        p.tail_rows_per_helper = (tail_smem - tail_bookkeeping_bytes(c.d, a->m) >= 2 * row_bytes_tail) ? 2 : 1;
+    }
     if (tensor_kernel) return launch_decode_tc(mk, mv, p, st);
     if (c.d == 256) return c.fp8 ? launch_decode<256, true>(mk, mv, p, st) : launch_decode<256, false>(mk, mv, p, st);
     return c.fp8 ? launch_decode<128, true>(mk, mv, p, st) : launch_decode<128, false>(mk, mv, p, st);

@@ -43,7 +43,8 @@ constexpr int TC_OFF_SC = TC_OFF_P + 2 * TC_P_BYTES;               // [KSLOTS][2
 constexpr int TC_OFF_ST = TC_OFF_SC + TC_KSLOTS * 2 * TC_BN * 4;   // per-row statistics, see below
 constexpr int TC_ST_FLOATS = 2 * 4 * 48 + 2 * 48 + 8;
 constexpr int TC_OFF_BAR = TC_OFF_ST + TC_ST_FLOATS * 4;
-constexpr int TC_SMEM = TC_OFF_BAR + 256 + 1024;
+constexpr int TC_OFF_TL = TC_OFF_BAR + 256;                        // timeline stamps (diagnostic build only)
+constexpr int TC_SMEM = TC_OFF_TL + 128 + 1024;
 constexpr int TC_TMEM_COLS = 512;
 constexpr int TC_TMEM_S = 0;                   // S^T buffers at columns 0 and 128
 constexpr int TC_TMEM_O = 256;                 // O^T accumulators (dims 0-127, 128-255) at columns 256 and 384
@@ -82,6 +83,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 
     const int split = blockIdx.x, j = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    unsigned long long *sm_tl = reinterpret_cast<unsigned long long *>(smem + TC_OFF_TL);
+    (void)sm_tl;
+    TRB_TL(sm_tl, 0);
 
     // ---- dependency plan (see decode_kernel) ----
     const int flags = p.pdl_flags;
@@ -129,6 +133,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    TRB_TL(sm_tl, 1);
 
     // producer helpers (the TMA warp)
     auto issue_k = [&](int i) {
@@ -169,6 +174,9 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         if (ns < 0) ns = 0;
         if (ns < n_stable) n_stable = (int)ns;
     }
+    // with a workspace of its own the CTA takes its ticket at its start (see decode_kernel)
+    if (warp == W_TMA && lane == 0 && (flags & PDL_PRIVATE_WS))
+        decode_ticket(p, j, active, NTHREADS / (D / 4), sm_flag, decode_ticket_take(p, j));
     int pre = 0;
     if (warp == W_TMA)
         while (pre < my_tiles && pre < 2 && pre < n_stable) { issue_k(pre); issue_v(pre); ++pre; }
@@ -227,6 +235,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     }
     fence_async_smem();
     __syncthreads();
+    TRB_TL(sm_tl, 3);
 
     bool ok = true;
     if (warp == W_TMA) {
@@ -240,8 +249,10 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         }
         // this warp is idle from here on: it takes the kv head's ticket (a workspace that an earlier
         // launch may still use: after the wait)
-        if (!(flags & PDL_PRIVATE_WS)) dep_wait();
-        if (lane == 0) decode_ticket(p, j, active, NTHREADS / (D / 4), sm_flag, decode_ticket_take(p, j));
+        if (!(flags & PDL_PRIVATE_WS)) {
+            dep_wait();
+            if (lane == 0) decode_ticket(p, j, active, NTHREADS / (D / 4), sm_flag, decode_ticket_take(p, j));
+        }
         named_barrier(15, NTHREADS);
     } else if (warp == W_MMA) {
         // ================================ MMA issuer ==================================
@@ -338,6 +349,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
                 if (barrier_or(bar_id, 128, false)) named_barrier(bar_id, 128);
                 continue;
             }
+            if (i == 0) TRB_TL(sm_tl, 4);
             tc_fence_after();
             float tv[16];
             {
@@ -444,10 +456,13 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         }
         // ---- epilogue: this CTA's partial rows.  acc[row][dim] = (hi + lo part of O^T[dim][row]) / 128
         ok = !dead;
+        TRB_TL(sm_tl, 5);
         if (ok && my_tiles > 0) ok = mbar_wait(&pv_done[(my_tiles - 1) & 1], ((my_tiles - 1) >> 1) & 1);
         tc_fence_after();
+        TRB_TL(sm_tl, 6);
         if (!(flags & PDL_PRIVATE_WS)) dep_wait();                             // the workspace belongs to this launch now
         named_barrier(15, NTHREADS);                                           // the ticket (taken by the producer warp) is in sm_flag
+        TRB_TL(sm_tl, 7);
         const unsigned int tag = (unsigned int)sm_flag[2] + 1u;
         const long long part_base = ((long long)j * p.nsplit + split) * p.rows_pad;
 #pragma unroll 1
@@ -518,7 +533,11 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     if (!(flags & PDL_PRIVATE_WS)) dep_wait();
     __syncthreads();
     if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem, TC_TMEM_COLS); }
-    decode_tail<D, NTHREADS>(p, smem, sm_flag, j, active);
+    TRB_TL(sm_tl, 8);
+    TRB_TL_SET(sm_tl, 13, sm_flag[0]);
+    TRB_TL_SET(sm_tl, 14, my_tiles);
+    decode_tail_teams<D, NTHREADS>(p, smem, sm_flag, j, active, sm_tl);
+    TRB_TL_FLUSH(sm_tl, (unsigned int)sm_flag[2], j * p.nsplit + split);
 }
 
 }  // namespace trb

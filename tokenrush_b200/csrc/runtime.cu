@@ -123,7 +123,8 @@ int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *po
             if (writers == 0) flags |= PDL_ALL_STABLE;
             if (q_clean) flags |= PDL_PRE_Q;
             if (mode == 2) flags |= PDL_TRIGGER_TOP;
-            if (mode == 2 && ws_free) flags |= PDL_PRIVATE_WS;
+            static const bool run_ahead = !(getenv("TRB_RUNAHEAD") && getenv("TRB_RUNAHEAD")[0] == '0');   // (for measurements)
+            if (mode == 2 && ws_free && run_ahead) flags |= PDL_PRIVATE_WS;
             // In a chain, the m rows of the one append in flight need not be awaited in the cache: the
             // decode quantises them from the append's own source rows (same arithmetic, same values)
             // and merges them as one more partial, while the scan covers the rows below the cursor.

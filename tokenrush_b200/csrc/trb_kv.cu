@@ -7,3 +7,4 @@
 #include "p2p.cu"
 #include "decode.cu"
 #include "prefill.cu"
+#include "norm.cu"

@@ -6,6 +6,7 @@ argument meaning, backed by the sm_100a CUDA library through its C ABI.
     attn_decode_fused    tokenrush/fused.py:449-470
     attn_prefill_fused   tokenrush/fused.py:523-533
     attn_window_block    tokenrush/fused.py:600-622
+    add_rmsnorm          tokenrush/fused.py:48-60    (the step after the attention output projection)
 
 plus the cursor arithmetic the reference does with small torch ops (`spec_commit`,
 tokenrush/model.py:306-312) and the ring write of the DFlash draft cache (`ring_write`,
@@ -95,11 +96,15 @@ def _workspace(device, hq: int, hkv: int, d: int, m: int):
         if n == 0:
             raise ValueError(f"unsupported geometry hq={hq} hkv={hkv} d={d} m={m}")
         n = (n + 255) // 256 * 256
-        ent = [torch.zeros(WORKSPACE_SLOTS * n, device=device, dtype=torch.uint8), n, 0]
+        # rotation only pays for the calls that can run ahead of the call before them (one 8-row slice:
+        # two of their CTAs share an SM); the partials of wider calls are large, and one workspace
+        # that stays in L2 serves them better than sixteen that do not
+        slots = WORKSPACE_SLOTS if (hq // hkv) * m <= 8 else 1
+        ent = [torch.zeros(slots * n, device=device, dtype=torch.uint8), n, 0]
         _workspaces[key] = ent
     buf, n, count = ent
     ent[2] = count + 1
-    return buf.data_ptr() + (count % WORKSPACE_SLOTS) * n, n
+    return buf.data_ptr() + (count % (buf.numel() // n)) * n, n
 
 
 def workspace_tensor(device, hq: int, hkv: int, d: int, m: int):
@@ -260,6 +265,36 @@ def attn_prefill_fused(q, k_cache, v_cache, pos, cfg, k_scale=None, v_scale=None
     L.check(L.lib().trb_attn_prefill(C.byref(cache), q.data_ptr(), o.data_ptr(), T, HQ, int(pos), float(D ** -0.5), _stream()),
             "trb_attn_prefill")
     return o
+
+
+# ------------------------------------------------------------------------------ after attention
+
+def add_rmsnorm(x: torch.Tensor, h, weight: torch.Tensor, eps: float, plain: bool = False):
+    """x [T, N] bf16; h None, [T, N] bf16, or [S, T, N] fp32 partials ->
+    (x + h as bf16, rmsnorm(x + h)); with h None -> (x, rmsnorm(x)).
+    plain: Qwen3's weight * x gain (the DFlash draft) instead of Qwen3.5's (1 + weight).
+    (tokenrush/fused.py:48-60; the attention output of attn_decode_fused reaches it through the
+    output projection: tokenrush/model.py:119-120.)"""
+    _need_cuda(x, h, weight)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not x.is_contiguous() or x.dim() != 2:
+        raise ValueError("x must be contiguous bf16 [T, N], weight bf16 [N]")
+    T, N = x.shape
+    y = torch.empty_like(x)
+    if h is None:
+        xo, splits, hp = x, 0, None
+    else:
+        if not h.is_contiguous():
+            raise ValueError("h must be contiguous")
+        if h.dim() == 2 and h.dtype == torch.bfloat16 and h.shape == x.shape:
+            splits = -1
+        elif h.dim() == 3 and h.dtype == torch.float32 and tuple(h.shape[1:]) == (T, N):
+            splits = h.shape[0]
+        else:
+            raise ValueError("h must be [T, N] bf16 or [S, T, N] fp32")
+        xo, hp = torch.empty_like(x), h.data_ptr()
+    L.check(L.lib().trb_add_rmsnorm(x.data_ptr(), hp, splits, weight.data_ptr(), float(eps), int(plain), T, N,
+                                    xo.data_ptr() if h is not None else None, y.data_ptr(), _stream()), "trb_add_rmsnorm")
+    return xo, y
 
 
 # ------------------------------------------------------------------------------ cursors
