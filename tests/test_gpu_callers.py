@@ -2,6 +2,8 @@
 of `attn_forward` (prep -> decode with gate, tokenrush/model.py:116-120), the MTP head's rewind
 (`set_pos`, tokenrush/mtp.py:84-87), a graph-captured DFlash draft step (ring write with a device
 valid count + window attention, tokenrush/dflash.py:293-299), and the `ops.py` callables."""
+import os
+
 import numpy as np
 import pytest
 import torch

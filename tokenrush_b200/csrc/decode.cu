@@ -1541,16 +1541,23 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     AppendSource fresh;
     p.pdl_flags = pdl_plan_decode(st, c.k, &a->pos, p.new_rows, a->m, WrittenRange{a->q, out_rows * c.d * sizeof(__nv_bfloat16)}, outs,
                                   a->workspace, &fresh);
-    p.fresh_k = (const __nv_bfloat16 *)fresh.k; p.fresh_v = (const __nv_bfloat16 *)fresh.v;
-    p.fresh_hs = fresh.head_stride; p.fresh_rs = fresh.row_stride;
-    if (p.fresh_k) p.new_rows = 0;                            // the scan covers the rows below the cursor, all visible to every row
+    // The tensor-core kernel fills an SM alone: CTAs that ran ahead of the launch before would start
+    // and finish far apart, and its helpers would sit on their SMs waiting for the stragglers.  Its
+    // CTAs (and the full-size CTAs of the several-slice kernel) therefore all wait before the
+    // epilogue and finish together.
+    if (tensor_kernel || p.nt != 1) p.pdl_flags &= ~PDL_PRIVATE_WS;
+    // Only the launches that run ahead of the launch before them (one slice, half-size CTAs) take the
+    // new rows from the append's source: the others wait for the append anyway before their epilogue.
+    p.fresh_k = p.fresh_v = nullptr; p.fresh_hs = p.fresh_rs = 0;
+    if (fresh.k && !tensor_kernel && p.nt == 1 && (p.pdl_flags & PDL_PRIVATE_WS)) {
+        p.fresh_k = (const __nv_bfloat16 *)fresh.k; p.fresh_v = (const __nv_bfloat16 *)fresh.v;
+        p.fresh_hs = fresh.head_stride; p.fresh_rs = fresh.row_stride;
+        p.new_rows = 0;                                       // the scan covers the rows below the cursor, all visible to every row
+        p.pdl_flags |= PDL_ALL_STABLE;                        // ... and all complete
+    }
     // a ring cache maps several positions to one row: the rows below the cursor are not the rows
     // below the in-flight append
     if (c.ring > 0 && !(p.pdl_flags & PDL_ALL_STABLE)) p.pdl_flags &= (PDL_TRIGGER_TOP | PDL_PRIVATE_WS);
-    // The tensor-core kernel fills an SM alone: CTAs that ran ahead of the launch before would start
-    // and finish far apart, and its helpers would sit on their SMs waiting for the stragglers.  Its
-    // CTAs therefore all wait before the epilogue and finish together.
-    if (tensor_kernel || p.nt != 1) p.pdl_flags &= ~PDL_PRIVATE_WS;   // (likewise the full-size CTAs of the several-slice kernel)
     p.tail_teams = tensor_kernel ? 1 : 0;
     p.kw = decode_warps(p) / (p.nt * (2 / decode_groups_per_warp(p.nt)));
     {   // a helper merges several rows when its tail can hold two rows' partials (the next row's copies fly during a merge)

@@ -134,7 +134,7 @@ int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *po
                 for (const InFlight &e : t.s)
                     for (const WrittenRange &w : e.w)
                         if (overlaps(w, sk) || overlaps(w, sv)) src_clean = false;
-                if (src_clean) { *fresh = writer->src; flags |= PDL_ALL_STABLE; }
+                if (src_clean) *fresh = writer->src;             // (a caller that takes them may treat every scanned row as complete)
             }
         }
     }
