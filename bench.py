@@ -589,6 +589,7 @@ def run_profile_case(args):
     import tokenrush_b200 as tb
     kind = WORKLOADS[args.workload]["profile"]
     f8 = torch.float8_e4m3fn
+    tb.fused.set_launch_mode(args.launch_mode)              # chained: every launch after the first takes the half-size CTAs
     if kind == "decode":
         rows = args.rows or 131072
         cfg = tb.AttnConfig(n_attn=args.layers)

@@ -178,6 +178,11 @@ typedef struct trb_decode_args {
      * their workspaces: the launch count of the workspace tags the exchange.               */
     void *const *p2p_xchg;
     int32_t     p2p_world, p2p_rank;
+    /* A caller that rotates over several workspaces (so that consecutive calls never share one) says
+     * which one this is: workspace number ws_slot of ws_slots, used strictly in turn.  The exchange
+     * between GPUs is then tagged with launch count of this workspace * ws_slots + ws_slot, i.e. with
+     * the call count of the whole rotation.  0 / 0 (or ws_slots = 1): a single workspace.            */
+    int32_t     ws_slot, ws_slots;
 } trb_decode_args_t;
 
 /* Precondition on the cache: the kernels load whole tiles (32 or 128 rows), so rows beyond the

@@ -40,7 +40,8 @@ class DecodeArgs(C.Structure):
                 ("extra_ml", C.c_void_p), ("extra_acc", C.c_void_p),
                 ("pos", Cursor), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
                 ("partial_ml", C.c_void_p), ("partial_acc", C.c_void_p),
-                ("p2p_xchg", C.c_void_p), ("p2p_world", C.c_int32), ("p2p_rank", C.c_int32)]
+                ("p2p_xchg", C.c_void_p), ("p2p_world", C.c_int32), ("p2p_rank", C.c_int32),
+                ("ws_slot", C.c_int32), ("ws_slots", C.c_int32)]
 
 
 class P2PMergeArgs(C.Structure):

@@ -64,6 +64,7 @@ struct DecodeParams {
     int sharded;
     int tail_rows_per_helper;     // output rows merged by one helper CTA (several when its shared memory holds two rows' partials)
     int tail_teams;               // the launch ends with decode_tail_teams (tensor-core kernel)
+    unsigned int xtag_mul, xtag_add;  // exchange tag = workspace epoch * xtag_mul + xtag_add + 1 (rotation of workspaces)
     int pdl_flags;                // PDL_*: what this launch may touch before its dependency wait
     // rows pos .. pos + m - 1 taken from the source rows of the append that is still writing them
     // (fresh_k == nullptr: they are read from the cache like every other row)
@@ -444,11 +445,13 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
             // (a GPU cannot be more than one call ahead of a peer whose packets it waits for).  This
             // GPU's own partial stays in registers.
             const P2PLayout xl = p2p_layout(p.p2p_world, p.m * p.hq, D);
-            const size_t slot = tag % P2P_SLOTS;
+            // the exchange counts the calls on this GPU's rotation of workspaces: every GPU makes the same calls
+            const unsigned int xtag = ((unsigned int)sm_flag[2]) * p.xtag_mul + p.xtag_add + 1u;
+            const size_t slot = xtag % P2P_SLOTS;
             const size_t nrow = (size_t)(p.m * p.hq);
-            const uint4 k0 = make_uint4(__float_as_uint(o.x), tag, __float_as_uint(o.y), tag);
-            const uint4 k1 = make_uint4(__float_as_uint(o.z), tag, __float_as_uint(o.w), tag);
-            const uint4 k2 = make_uint4(__float_as_uint(mmax), tag, __float_as_uint(lsum), tag);
+            const uint4 k0 = make_uint4(__float_as_uint(o.x), xtag, __float_as_uint(o.y), xtag);
+            const uint4 k1 = make_uint4(__float_as_uint(o.z), xtag, __float_as_uint(o.w), xtag);
+            const uint4 k2 = make_uint4(__float_as_uint(mmax), xtag, __float_as_uint(lsum), xtag);
             for (int r = 0; r < p.p2p_world; ++r) {
                 if (r == p.p2p_rank) continue;
                 uint4 *dst = reinterpret_cast<uint4 *>((uint8_t *)p.p2p_ptr[r] + xl.ll) +
@@ -468,7 +471,7 @@ __device__ __forceinline__ void decode_tail(const DecodeParams &p, uint8_t *smem
                     if (!((pending >> r) & 1u)) continue;
                     const uint4 *src = local + (((slot * p.p2p_world + r) * nrow + grow) * ITEMS + item) * 3;
                     const uint4 b0 = ld_volatile_v4(src), b1 = ld_volatile_v4(src + 1), b2 = ld_volatile_v4(src + 2);
-                    if (b0.y == tag && b0.w == tag && b1.y == tag && b1.w == tag && b2.y == tag && b2.w == tag) {
+                    if (b0.y == xtag && b0.w == xtag && b1.y == xtag && b1.w == xtag && b2.y == xtag && b2.w == xtag) {
                         pk[r][0] = b0; pk[r][1] = b1; pk[r][2] = b2;
                         pending &= ~(1u << r);
                     }
@@ -720,11 +723,13 @@ __device__ __forceinline__ void decode_tail_teams(const DecodeParams &p, uint8_t
             // (a GPU cannot be more than one call ahead of a peer whose packets it waits for).  This
             // GPU's own partial stays in registers.
             const P2PLayout xl = p2p_layout(p.p2p_world, p.m * p.hq, D);
-            const size_t slot = tag % P2P_SLOTS;
+            // the exchange counts the calls on this GPU's rotation of workspaces: every GPU makes the same calls
+            const unsigned int xtag = ((unsigned int)sm_flag[2]) * p.xtag_mul + p.xtag_add + 1u;
+            const size_t slot = xtag % P2P_SLOTS;
             const size_t nrow = (size_t)(p.m * p.hq);
-            const uint4 k0 = make_uint4(__float_as_uint(o.x), tag, __float_as_uint(o.y), tag);
-            const uint4 k1 = make_uint4(__float_as_uint(o.z), tag, __float_as_uint(o.w), tag);
-            const uint4 k2 = make_uint4(__float_as_uint(mmax), tag, __float_as_uint(lsum), tag);
+            const uint4 k0 = make_uint4(__float_as_uint(o.x), xtag, __float_as_uint(o.y), xtag);
+            const uint4 k1 = make_uint4(__float_as_uint(o.z), xtag, __float_as_uint(o.w), xtag);
+            const uint4 k2 = make_uint4(__float_as_uint(mmax), xtag, __float_as_uint(lsum), xtag);
             for (int r = 0; r < p.p2p_world; ++r) {
                 if (r == p.p2p_rank) continue;
                 uint4 *dst = reinterpret_cast<uint4 *>((uint8_t *)p.p2p_ptr[r] + xl.ll) +
@@ -744,7 +749,7 @@ __device__ __forceinline__ void decode_tail_teams(const DecodeParams &p, uint8_t
                     if (!((pending >> r) & 1u)) continue;
                     const uint4 *src = local + (((slot * p.p2p_world + r) * nrow + grow) * ITEMS + item) * 3;
                     const uint4 b0 = ld_volatile_v4(src), b1 = ld_volatile_v4(src + 1), b2 = ld_volatile_v4(src + 2);
-                    if (b0.y == tag && b0.w == tag && b1.y == tag && b1.w == tag && b2.y == tag && b2.w == tag) {
+                    if (b0.y == xtag && b0.w == xtag && b1.y == xtag && b1.w == xtag && b2.y == xtag && b2.w == xtag) {
                         pk[r][0] = b0; pk[r][1] = b1; pk[r][2] = b2;
                         pending &= ~(1u << r);
                     }
@@ -1517,6 +1522,9 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     p.part_ml = (uint4 *)(ws + w.ml); p.part_acc = (uint2 *)(ws + w.acc);
     p.shard_ml = a->partial_ml; p.shard_acc = a->partial_acc;
     p.p2p_world = 0; p.p2p_rank = 0;
+    p.xtag_mul = a->ws_slots > 1 ? (unsigned int)a->ws_slots : 1u;
+    p.xtag_add = a->ws_slots > 1 ? (unsigned int)a->ws_slot : 0u;
+    if (a->ws_slots > 1 && (a->ws_slot < 0 || a->ws_slot >= a->ws_slots)) return TRB_E_ARG;
     for (int r = 0; r < 8; ++r) p.p2p_ptr[r] = nullptr;
     if (a->p2p_xchg) {
         if (a->p2p_world < 1 || a->p2p_world > P2P_MAX_WORLD || a->p2p_rank < 0 || a->p2p_rank >= a->p2p_world || a->partial_acc) return TRB_E_ARG;
@@ -1558,7 +1566,8 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     // a ring cache maps several positions to one row: the rows below the cursor are not the rows
     // below the in-flight append
     if (c.ring > 0 && !(p.pdl_flags & PDL_ALL_STABLE)) p.pdl_flags &= (PDL_TRIGGER_TOP | PDL_PRIVATE_WS);
-    p.tail_teams = tensor_kernel ? 1 : 0;
+    static const bool tc_bulk_tail = getenv("TRB_TC_TAIL") && getenv("TRB_TC_TAIL")[0] == 'b';   // (for measurements)
+    p.tail_teams = (tensor_kernel && !tc_bulk_tail) ? 1 : 0;
     p.kw = decode_warps(p) / (p.nt * (2 / decode_groups_per_warp(p.nt)));
     {   // a helper merges several rows when its tail can hold two rows' partials (the next row's copies fly during a merge)
         const int tail_smem = tensor_kernel ? TC_OFF_SC : decode_warps(p) * DEC_STAGE_BYTES_PER_WARP;

@@ -80,7 +80,7 @@ WORKSPACE_SLOTS = 16       # decode workspaces per (device, stream, geometry), u
 
 
 def _workspace(device, hq: int, hkv: int, d: int, m: int):
-    """Split-partial scratch + ticket words for one decode call: (device pointer, bytes).  Every
+    """Split-partial scratch + ticket words for one decode call: (device pointer, bytes, slot, slots).  Every
     (device, stream, geometry) owns WORKSPACE_SLOTS workspaces, zeroed once, and hands them out in
     rotation: consecutive decode calls of a step then never share one, which lets a call in a
     chain of library launches (launch mode 2) publish its partials without waiting for the call
@@ -104,7 +104,8 @@ def _workspace(device, hq: int, hkv: int, d: int, m: int):
         _workspaces[key] = ent
     buf, n, count = ent
     ent[2] = count + 1
-    return buf.data_ptr() + (count % (buf.numel() // n)) * n, n
+    slots = buf.numel() // n
+    return buf.data_ptr() + (count % slots) * n, n, count % slots, slots
 
 
 def workspace_tensor(device, hq: int, hkv: int, d: int, m: int):
@@ -173,7 +174,7 @@ def _decode(q, k_cache, v_cache, pos, HQ, HKV, D, k_scale, v_scale, *, gate=None
         raise ValueError("q must be contiguous bf16 [M, HQ*D]")
     M = q.shape[0]
     cache = _cache(k_cache, v_cache, k_scale, v_scale, ring, shard_lo)
-    ws_ptr, ws_bytes = _workspace(q.device, HQ, HKV, D, M)
+    ws_ptr, ws_bytes, ws_slot, ws_slots = _workspace(q.device, HQ, HKV, D, M)
     a = L.DecodeArgs()
     a.q = q.data_ptr()
     a.m, a.hq = M, HQ
@@ -181,6 +182,7 @@ def _decode(q, k_cache, v_cache, pos, HQ, HKV, D, k_scale, v_scale, *, gate=None
     a.new_rows, a.window = int(new_rows), int(window)
     a.pos = _cursor(pos)
     a.workspace, a.workspace_bytes = ws_ptr, ws_bytes
+    a.ws_slot, a.ws_slots = ws_slot, ws_slots
     if gate is not None:
         a.gate, a.gate_row_stride, a.gate_head_stride = gate, gate_rs, gate_hs
     if extra is not None:
