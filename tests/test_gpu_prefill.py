@@ -87,3 +87,21 @@ def test_prefill_peaked_scores(tb):
     kd, vd = ref.dequant(0, pos + T)
     want = O.attn_prefill(O.bf16_bits_to_f32(qb), kd, vd, pos)
     assert_attn_close(f32_of(o), want, "peaked prefill")
+
+
+@pytest.mark.parametrize("hq,hkv,d,pos,T", [(24, 4, 256, 37, 150), (32, 8, 128, 37, 150), (24, 4, 256, 0, 9)])
+def test_prefill_over_a_bf16_cache(tb, hq, hkv, d, pos, T):
+    """The reference's attn_prefill_fused defaults to a bf16 cache and its own test pins that mode at
+    pos 37, T 150 (tests/test_fused.py:265-276).  The same call on a bf16 State, at both head
+    geometries of the reference's tests, against fp32 oracle attention over the bf16 rows."""
+    from types import SimpleNamespace
+    cfg = SimpleNamespace(n_heads=hq, n_kv_heads=hkv, head_dim=d, attn_layers=[0])
+    kb, vb = O.seeded_bf16(701, hkv, pos + T, d), O.seeded_bf16(702, hkv, pos + T, d)
+    qb = O.seeded_bf16(703, T, hq, d)
+    st = tb.State(cfg, pos + T + 40, "cuda", kv_dtype=torch.bfloat16)
+    tb.fused.kv_write_prefill(to_dev(kb), to_dev(vb), st, 0, 0)      # bf16 cache: rows stored as they are
+    o = tb.fused.attn_prefill_fused(to_dev(qb), st.k[0], st.v[0], pos, cfg)
+    assert o.shape == (T, hq, d) and o.dtype == torch.bfloat16
+    want = O.attn_prefill(O.bf16_bits_to_f32(qb), O.bf16_bits_to_f32(kb), O.bf16_bits_to_f32(vb), pos)
+    assert_attn_close(f32_of(o), want, f"bf16 cache hq={hq} d={d} pos={pos} T={T}")
+    assert tb._lib.device_status() == 0

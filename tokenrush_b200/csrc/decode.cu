@@ -1566,8 +1566,7 @@ extern "C" int trb_attn_decode(const trb_cache_t *cache, const trb_decode_args_t
     // a ring cache maps several positions to one row: the rows below the cursor are not the rows
     // below the in-flight append
     if (c.ring > 0 && !(p.pdl_flags & PDL_ALL_STABLE)) p.pdl_flags &= (PDL_TRIGGER_TOP | PDL_PRIVATE_WS);
-    static const bool tc_bulk_tail = getenv("TRB_TC_TAIL") && getenv("TRB_TC_TAIL")[0] == 'b';   // (for measurements)
-    p.tail_teams = (tensor_kernel && !tc_bulk_tail) ? 1 : 0;
+    p.tail_teams = tensor_kernel ? 1 : 0;
     p.kw = decode_warps(p) / (p.nt * (2 / decode_groups_per_warp(p.nt)));
     {   // a helper merges several rows when its tail can hold two rows' partials (the next row's copies fly during a merge)
         const int tail_smem = tensor_kernel ? TC_OFF_SC : decode_warps(p) * DEC_STAGE_BYTES_PER_WARP;

@@ -536,8 +536,7 @@ decode_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     TRB_TL(sm_tl, 8);
     TRB_TL_SET(sm_tl, 13, sm_flag[0]);
     TRB_TL_SET(sm_tl, 14, my_tiles);
-    if (p.tail_teams) decode_tail_teams<D, NTHREADS>(p, smem, sm_flag, j, active, sm_tl);
-    else decode_tail<D, NTHREADS>(p, smem, TC_OFF_SC, sm_flag, j, active, sm_tl);
+    decode_tail_teams<D, NTHREADS>(p, smem, sm_flag, j, active, sm_tl);
     TRB_TL_FLUSH(sm_tl, (unsigned int)sm_flag[2], j * p.nsplit + split);
 }
 

@@ -263,6 +263,18 @@ def attn_prefill_fused(q, k_cache, v_cache, pos, cfg, k_scale=None, v_scale=None
     if q.dtype != torch.bfloat16 or not q.is_contiguous():
         raise ValueError("q must be contiguous bf16 [T, HQ, D]")
     cache = _cache(k_cache, v_cache, k_scale, v_scale)
+    if k_cache.dtype == torch.bfloat16:
+        # The tensor-core prefill kernel reads the fp8 cache only.  A bf16 cache (the reference's default,
+        # tokenrush/fused.py:523-533 with FP8 = False) goes through the M-row decode kernel, whose bf16
+        # path reads the cache with ldmatrix, in groups of as many rows as one launch takes.
+        HKV = k_cache.shape[0]
+        m_max = max(1, 48 // (HQ // HKV))
+        o = torch.empty_like(q)
+        for s0 in range(0, T, m_max):
+            m = min(m_max, T - s0)
+            _decode(q[s0:s0 + m].reshape(m, HQ * D), k_cache, v_cache, int(pos) + s0, HQ, HKV, D, None, None, new_rows=1,
+                    out=o[s0:s0 + m].view(m, HQ * D))
+        return o
     o = torch.empty_like(q)
     L.check(L.lib().trb_attn_prefill(C.byref(cache), q.data_ptr(), o.data_ptr(), T, HQ, int(pos), float(D ** -0.5), _stream()),
             "trb_attn_prefill")
