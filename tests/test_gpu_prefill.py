@@ -103,5 +103,8 @@ def test_prefill_over_a_bf16_cache(tb, hq, hkv, d, pos, T):
     o = tb.fused.attn_prefill_fused(to_dev(qb), st.k[0], st.v[0], pos, cfg)
     assert o.shape == (T, hq, d) and o.dtype == torch.bfloat16
     want = O.attn_prefill(O.bf16_bits_to_f32(qb), O.bf16_bits_to_f32(kb), O.bf16_bits_to_f32(vb), pos)
-    assert_attn_close(f32_of(o), want, f"bf16 cache hq={hq} d={d} pos={pos} T={T}")
+    # over a bf16 cache the probabilities enter the PV product as bf16 (as in the reference's kernel:
+    # `p.to(tl.bfloat16)`, tokenrush/fused.py:515), so with only a few visible keys an element carries
+    # that rounding on top of the bf16 rounding of the output: two steps of 2^-8 instead of one
+    assert_attn_close(f32_of(o), want, f"bf16 cache hq={hq} d={d} pos={pos} T={T}", out_ulp=2.0 ** -7)
     assert tb._lib.device_status() == 0
