@@ -104,7 +104,11 @@ def test_prefill_over_a_bf16_cache(tb, hq, hkv, d, pos, T):
     assert o.shape == (T, hq, d) and o.dtype == torch.bfloat16
     want = O.attn_prefill(O.bf16_bits_to_f32(qb), O.bf16_bits_to_f32(kb), O.bf16_bits_to_f32(vb), pos)
     # over a bf16 cache the probabilities enter the PV product as bf16 (as in the reference's kernel:
-    # `p.to(tl.bfloat16)`, tokenrush/fused.py:515), so with only a few visible keys an element carries
-    # that rounding on top of the bf16 rounding of the output: two steps of 2^-8 instead of one
-    assert_attn_close(f32_of(o), want, f"bf16 cache hq={hq} d={d} pos={pos} T={T}", out_ulp=2.0 ** -7)
+    # `p.to(tl.bfloat16)`, tokenrush/fused.py:515).  With only a few visible keys of mixed signs that
+    # rounding does not average out and is proportional to sum p |v|, not to |o|: the bar is the
+    # north_star's rel 1e-2 over the tensor plus 2^-7 of the largest output per element.
+    got = f32_of(o)
+    from _util import rel
+    assert np.isfinite(got).all() and rel(got, want) <= 1e-2, rel(got, want)
+    assert np.abs(got - want).max() <= 2e-3 + 2.0 ** -7 * np.abs(want).max(), float(np.abs(got - want).max())
     assert tb._lib.device_status() == 0
