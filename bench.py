@@ -24,6 +24,8 @@ Workloads (synthetic: N(0,1) values quantised into the FP8 cache layout, seeded)
                  small, self-ending cases of one kernel for a profiler (--rows, --m, --t)
     timeline     per-phase time stamps of the M = 1 decode kernel's CTAs (needs the diagnostic
                  library: python -m tokenrush_b200.build --timeline), --rows live rows, 16 layers
+    timeline-prefill   clock stamps of the prefill kernel's softmax and MMA warps over 32 key tiles of one
+                 query block (same library), --rows cached rows, --t new tokens, --kv fp8|bf16
 Inputs are far larger than L2 (126 MB), so consecutive steps cannot be served from cache.
 
 The default single-GPU run reports window256k as the headline and attaches short runs of ctx32k,
@@ -63,6 +65,7 @@ WORKLOADS = {
     "prefill8k": dict(ctx=131072, t=8192),
     "profile-decode": dict(profile="decode"),
     "profile-prefill": dict(profile="prefill"),
+    "timeline-prefill": dict(profile="prefill-timeline"),
     "timeline": dict(profile="timeline"),
 }
 # DRAM bytes moved per live row by one launch of the decode kernels (dram__bytes_read.sum +
@@ -144,7 +147,7 @@ def fill_cache_(state, seed: int):
             k = torch.randn(hkv, t, d, device="cuda", generator=g).to(torch.bfloat16)
             v = torch.randn(hkv, t, d, device="cuda", generator=g).to(torch.bfloat16)
             tb.fused.kv_append(k, v, state.k[slot], state.v[slot], state.shard_lo + p0 if state.shard_lo is not None else p0,
-                               state.k_scale[slot], state.v_scale[slot], shard_lo=state.shard_lo)
+                               state.k_scale[slot] if state.fp8 else None, state.v_scale[slot] if state.fp8 else None, shard_lo=state.shard_lo)
     torch.cuda.synchronize()
 
 
@@ -165,8 +168,12 @@ def _oracle_layer(state, slot: int, heads, n_rows: int):
     """One layer of a CUDA State as an OracleState holding rows [0, n_rows) of the kv heads listed
     (the other heads stay zero: they are not evaluated)."""
     from oracle import kv_oracle as O
-    st = O.OracleState(1, HKV, max(n_rows, 1), D)
+    st = O.OracleState(1, HKV, max(n_rows, 1), D, fp8=state.fp8)
     for j in heads:
+        if not state.fp8:
+            st.k[0, j] = state.k[slot, j, :n_rows].view(torch.int16).cpu().numpy().view("uint16")
+            st.v[0, j] = state.v[slot, j, :n_rows].view(torch.int16).cpu().numpy().view("uint16")
+            continue
         st.k[0, j] = state.k[slot, j, :n_rows].view(torch.uint8).cpu().numpy()
         st.v[0, j] = state.v[slot, j, :n_rows].view(torch.uint8).cpu().numpy()
         st.k_scale[0, j] = state.k_scale[slot, j, :n_rows].cpu().numpy()
@@ -488,8 +495,10 @@ def run_prefill(name: str, args, steps: int, warmup: int):
     pos, t = wl["ctx"], wl["t"]
     steps, warmup = max(1, min(steps, 10)), max(1, min(warmup, 3))
     cfg = tb.AttnConfig(n_attn=LAYERS)
-    state = tb.State(cfg, pos + t + 64, "cuda", kv_dtype=torch.float8_e4m3fn)
+    fp8 = args.kv == "fp8"
+    state = tb.State(cfg, pos + t + 64, "cuda", kv_dtype=torch.float8_e4m3fn if fp8 else torch.bfloat16)
     fill_cache_(state, seed=0)
+    scales = (lambda l: (state.k_scale[l], state.v_scale[l])) if fp8 else (lambda l: (None, None))
     gen = torch.Generator().manual_seed(0)
     h_q = torch.randn(t, HQ, D, generator=gen).to(torch.bfloat16).pin_memory()
     h_k = torch.randn(HKV, t, D, generator=gen).to(torch.bfloat16).pin_memory()
@@ -501,7 +510,7 @@ def run_prefill(name: str, args, steps: int, warmup: int):
     def step():
         for l in range(LAYERS):
             tb.fused.kv_write_prefill(d_k, d_v, state, l, pos)
-            outs[l] = tb.fused.attn_prefill_fused(d_q, state.k[l], state.v[l], pos, cfg, state.k_scale[l], state.v_scale[l])
+            outs[l] = tb.fused.attn_prefill_fused(d_q, state.k[l], state.v[l], pos, cfg, *scales(l))
 
     def timed(fn, n):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -524,7 +533,7 @@ def run_prefill(name: str, args, steps: int, warmup: int):
         for l in range(LAYERS):                                  # every layer's chunk comes from the host
             d_q.copy_(h_q, non_blocking=True); d_k.copy_(h_k, non_blocking=True); d_v.copy_(h_v, non_blocking=True)
             tb.fused.kv_write_prefill(d_k, d_v, state, l, pos)
-            o = tb.fused.attn_prefill_fused(d_q, state.k[l], state.v[l], pos, cfg, state.k_scale[l], state.v_scale[l])
+            o = tb.fused.attn_prefill_fused(d_q, state.k[l], state.v[l], pos, cfg, *scales(l))
             h_out.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()
     e2e_steps = max(1, steps // 2)
@@ -533,7 +542,7 @@ def run_prefill(name: str, args, steps: int, warmup: int):
 
     def attn_only():
         for l in range(LAYERS):
-            tb.fused.attn_prefill_fused(d_q, state.k[l], state.v[l], pos, cfg, state.k_scale[l], state.v_scale[l])
+            tb.fused.attn_prefill_fused(d_q, state.k[l], state.v[l], pos, cfg, *scales(l))
     ms_k = timed(attn_only, 1)
     peaks, how = measured_peaks()
     peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
@@ -545,6 +554,9 @@ def run_prefill(name: str, args, steps: int, warmup: int):
     exact = True
     for l in (0, LAYERS - 1):
         for src, cache, scale in ((kb, state.k, state.k_scale), (vb, state.v, state.v_scale)):
+            if not fp8:
+                exact &= bool(np.array_equal(cache[l, :, pos:pos + t].view(torch.int16).cpu().numpy().view(np.uint16), src))
+                continue
             codes, sc = O.quantize_rows(O.bf16_bits_to_f32(src))
             exact &= bool(np.array_equal(cache[l, :, pos:pos + t].view(torch.uint8).cpu().numpy(), codes))
             exact &= bool(np.array_equal(scale[l, :, pos:pos + t].cpu().numpy().view(np.uint32), sc.view(np.uint32)))
@@ -563,8 +575,8 @@ def run_prefill(name: str, args, steps: int, warmup: int):
     line = {
         "metric": "prefill_attn_tflops", "value": round(value, 1), "unit": "TFLOP/s", "ms_per_step": round(ms / steps, 3),
         "n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "fp8_e4m3 operands (q and p as hi+lo pairs), fp32 accumulate in TMEM", "data": "synthetic",
-        "config": {"workload": name, "layers": LAYERS, "cached_rows": pos, "new_tokens": t, "heads": f"{HQ}q/{HKV}kv x {D}",
+        "dtype": ("fp8_e4m3 operands (q and p as hi+lo pairs)" if fp8 else "bf16 operands") + ", fp32 accumulate in TMEM", "data": "synthetic",
+        "config": {"workload": name, "layers": LAYERS, "cached_rows": pos, "new_tokens": t, "heads": f"{HQ}q/{HKV}kv x {D}", "kv_cache": args.kv,
                    "flop_per_step": flops, "l2": "inputs larger than L2 (no flush needed)"},
         "e2e": {"value": round(e2e_value, 1), "unit": "TFLOP/s", "ms_per_step": round(ms_e2e / e2e_steps, 3),
                 "h2d_bytes_per_step": LAYERS * (h_q.numel() + h_k.numel() + h_v.numel()) * 2, "d2h_bytes_per_step": LAYERS * h_out.numel() * 2},
@@ -572,7 +584,7 @@ def run_prefill(name: str, args, steps: int, warmup: int):
         "clocks": clocks.summary(),
         "roofline": {"bound": "tensor", "kernel": "prefill_kernel", "achieved": round(achieved, 1), "peak": peak, "peak_source": how,
                      "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None,
-                     "note": "algorithmic flops (each product counted once); the kernel issues two e4m3 MMAs per product at the FP8 rate"},
+                     "note": "algorithmic flops (each product counted once); " + ("the kernel issues two e4m3 MMAs per product at the FP8 rate" if fp8 else "one bf16 MMA per product")},
         "cpu_baseline": {"value": round(cpu_flops / cpu_dt / 1e12, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": f"{len(rows)} query rows x {len(hq_sel)} heads of one layer over {pos + t} keys incl. dequantisation ({cpu_dt:.2f} s); it is also the parity check"},
         "parity": {"ok": bool(ok and exact), "layers": [0, LAYERS - 1], "kv_heads": list(heads), "sampled_query_rows": len(rows), "max_abs_err": max_abs,
@@ -603,12 +615,36 @@ def run_profile_case(args):
     else:
         rows = args.rows or 16384
         cfg = tb.AttnConfig(n_attn=1)
-        st = tb.State(cfg, rows + args.t + 64, "cuda", kv_dtype=f8)
-        random_fill_(st)
+        st = tb.State(cfg, rows + args.t + 64, "cuda", kv_dtype=f8 if args.kv == "fp8" else torch.bfloat16)
+        if st.fp8:
+            random_fill_(st)
+        else:
+            st.k.normal_(); st.v.normal_()
         q = torch.randn(args.t, HQ, D, device="cuda").to(torch.bfloat16)
         for _ in range(min(args.iters, 2)):
-            tb.fused.attn_prefill_fused(q, st.k[0], st.v[0], rows, cfg, st.k_scale[0], st.v_scale[0])
+            tb.fused.attn_prefill_fused(q, st.k[0], st.v[0], rows, cfg, st.k_scale[0] if st.fp8 else None, st.v_scale[0] if st.fp8 else None)
     torch.cuda.synchronize()
+    if kind == "prefill-timeline":
+        import ctypes as C
+        import numpy as np
+        lib = tb._lib.lib()
+        if not hasattr(lib, "trb_dbg_timeline"):
+            raise SystemExit("the loaded library has no timeline: build it with `python -m tokenrush_b200.build --timeline`")
+        lib.trb_dbg_timeline.argtypes, lib.trb_dbg_timeline.restype = [C.c_void_p, C.c_size_t], C.c_int
+        buf = np.zeros((64, 256, 16), dtype=np.uint64)
+        assert lib.trb_dbg_timeline(buf.ctypes.data, buf.nbytes) == 0
+        a = buf[63, :32].astype(np.int64)
+        t0 = a[0, 0]
+        names = ["sm pass start", "sm S ready", "sm S loaded", "sm max done", "sm barrier passed", "sm PV(i-1) done", "sm P written", "sm P published",
+                 "mma qk entry", "mma K landed", "mma S buffer free", "mma QK issued", "mma pv entry", "mma V landed", "mma P ready", "mma PV issued"]
+        print("clock64 cycles relative to the first stamp; one line per key tile (softmax warp 0, then the MMA warp)")
+        print(" | ".join(names))
+        for r in a:
+            print(" ".join(f"{int(v - t0):7d}" for v in r))
+        d = np.diff(a[:, 0])
+        print(json.dumps({"cycles_per_tile_median": float(np.median(d)), "softmax_pass_cycles_median": float(np.median(a[:, 7] - a[:, 0])),
+                          "kv": args.kv}))
+        return
     print(json.dumps({"profile_case": kind, "rows": rows, "device_status": tb._lib.device_status()}), flush=True)
 
 
@@ -975,6 +1011,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-extra", action="store_true", help="headline workload only (no `workloads` object)")
     ap.add_argument("--no-triton", action="store_true", help="reference arm: skip the reference's GPU kernels")
+    ap.add_argument("--kv", default="fp8", choices=["fp8", "bf16"], help="prefill workloads: cache dtype")
     ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--t", type=int, default=2048)
@@ -982,8 +1019,9 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--decode-only", action="store_true", help="timeline: a graph of the 16 decode launches without appends")
     args = ap.parse_args()
-    if args.workload == "timeline":
+    if args.workload.startswith("timeline"):
         os.environ["TRB_KV_LIB"] = os.path.join(ROOT, "tokenrush_b200", "libtrb_kv_timeline.so")   # read when the package is imported
+    if args.workload == "timeline":
         run_timeline(args)
     elif args.impl == "reference":
         run_reference(args)

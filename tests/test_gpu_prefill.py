@@ -89,11 +89,13 @@ def test_prefill_peaked_scores(tb):
     assert_attn_close(f32_of(o), want, "peaked prefill")
 
 
-@pytest.mark.parametrize("hq,hkv,d,pos,T", [(24, 4, 256, 37, 150), (32, 8, 128, 37, 150), (24, 4, 256, 0, 9)])
+@pytest.mark.parametrize("hq,hkv,d,pos,T", [(24, 4, 256, 37, 150), (32, 8, 128, 37, 150), (24, 4, 256, 0, 9), (24, 4, 256, 4113, 520), (8, 8, 256, 0, 1)])
 def test_prefill_over_a_bf16_cache(tb, hq, hkv, d, pos, T):
     """The reference's attn_prefill_fused defaults to a bf16 cache and its own test pins that mode at
     pos 37, T 150 (tests/test_fused.py:265-276).  The same call on a bf16 State, at both head
-    geometries of the reference's tests, against fp32 oracle attention over the bf16 rows."""
+    geometries of the reference's tests, against fp32 oracle attention over the bf16 rows.  256-dim heads
+    take the tensor-core kernel (bf16 MMAs; the longer case spans 73 key tiles and 5 query blocks),
+    128-dim heads the M-row decode kernel."""
     from types import SimpleNamespace
     cfg = SimpleNamespace(n_heads=hq, n_kv_heads=hkv, head_dim=d, attn_layers=[0])
     kb, vb = O.seeded_bf16(701, hkv, pos + T, d), O.seeded_bf16(702, hkv, pos + T, d)

@@ -52,15 +52,30 @@ struct PrefillParams {
     float scale_log2;
 };
 
+// FP8 = false: the same kernel over a bf16 cache (the reference's default mode, tokenrush/fused.py:523-533
+// with FP8 = False): K, V and Q feed tcgen05.mma kind::f16 as bf16 straight from the TMA tiles and
+// the staged query rows, the probabilities are staged as bf16; no scales, no hi + lo terms.  Rows are
+// 512 bytes (four 128-byte column blocks), tiles 32 KB, so two pipeline stages take the place of four.
+// Diagnostic build only: the last query block of head 0 stamps clock64 at fixed points of tiles 64..95
+// (slots 0-7: lane 0 of softmax warp 0, slots 8-15: lane 0 of the MMA warp) into timeline launch slot 63.
+#ifdef TRB_TIMELINE
+#define PF_TL(i, slot) do { if (lane == 0 && tl_on && (i) >= 64 && (i) < 96) g_timeline[63][(i) - 64][slot] = (unsigned long long)clock64(); } while (0)
+#else
+#define PF_TL(i, slot) do { } while (0)
+#endif
+
+template <bool FP8>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+    constexpr int ROWB = PF_D * (FP8 ? 1 : 2), SEGS = ROWB / 128, TILE = PF_BN * ROWB, STAGES = FP8 ? PF_STAGES : PF_STAGES / 2;
+    static_assert(STAGES * 2 * TILE == PF_STAGES * 2 * PF_TILE && (FP8 ? 2 : 1) * PF_BM * ROWB == 2 * PF_Q_BYTES, "shared-memory layout");
     extern __shared__ uint8_t pf_smem_raw[];
     uint8_t *smem = pf_smem_raw + ((1024u - (smem_u32(pf_smem_raw) & 1023u)) & 1023u);
     float *sm_sc = reinterpret_cast<float *>(smem + PF_OFF_SC);
     float *sm_fac = reinterpret_cast<float *>(smem + PF_OFF_FAC);
     float *sm_mx = reinterpret_cast<float *>(smem + PF_OFF_MX);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + PF_OFF_BAR);
-    uint64_t *kv_full = bars, *kv_free = bars + PF_STAGES;
+    uint64_t *kv_full = bars, *kv_free = bars + PF_STAGES;   // (STAGES of each are used)
     uint64_t *s_full = bars + 2 * PF_STAGES, *s_free = s_full + 2, *p_full = s_full + 4, *o_done = s_full + 5, *q_ready = s_full + 6;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_full + 7);
 
@@ -71,9 +86,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     // keys below `hi` can be seen by some row of this block
     const long long hi = p.pos + q0 + rows_here;
     const int n_tiles = (int)((hi + PF_BN - 1) / PF_BN);
+#ifdef TRB_TIMELINE
+    const bool tl_on = blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (warp == 0 || warp == 9);
+#endif
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PF_STAGES; ++s) { mbar_init(&kv_full[s], 33u); mbar_init(&kv_free[s], 1u); }
+        // FP8: one barrier pair per stage (K + V tile + 64 scale pairs).  bf16: the two stages' K tiles on
+        // barriers 0-1 and V tiles on 2-3, so that a K tile is refilled as soon as its QK^T has run
+        for (int s = 0; s < PF_STAGES; ++s) { mbar_init(&kv_full[s], FP8 ? 33u : 1u); mbar_init(&kv_free[s], 1u); }
         for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1u); mbar_init(&s_free[b], 8u); }
         mbar_init(p_full, 8u); mbar_init(o_done, 1u); mbar_init(q_ready, 8u);
         mbar_fence_init();
@@ -88,27 +108,44 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     if (warp == 8) {
         // ================================ TMA producer ================================
         for (int i = 0; i < n_tiles; ++i) {
-            const int s = i % PF_STAGES;
-            if (i >= PF_STAGES && !mbar_wait(&kv_free[s], ((i / PF_STAGES) & 1) ^ 1)) break;
+            const int s = i % STAGES;
             const int row0 = i * PF_BN;
-            uint8_t *kt = smem + PF_OFF_KV + s * 2 * PF_TILE, *vt = kt + PF_TILE;
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&kv_full[s], 2 * PF_TILE);
+            uint8_t *kt = smem + PF_OFF_KV + s * 2 * TILE, *vt = kt + TILE;
+            if constexpr (!FP8) {
+                const uint32_t par = ((i / STAGES) & 1) ^ 1;
+                if (i >= STAGES && !mbar_wait(&kv_free[s], par)) break;            // QK^T of tile i-2 has run
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&kv_full[s], TILE);
 #pragma unroll
-                for (int sg = 0; sg < 2; ++sg) {
-                    tma_load_4d(kt + sg * (PF_BN * 128), &tm_k, &kv_full[s], 0, sg, row0, j);
-                    tma_load_4d(vt + sg * (PF_BN * 128), &tm_v, &kv_full[s], 0, sg, row0, j);
+                    for (int sg = 0; sg < SEGS; ++sg) tma_load_4d(kt + sg * (PF_BN * 128), &tm_k, &kv_full[s], 0, sg, row0, j);
                 }
-            }
+                if (i >= STAGES && !mbar_wait(&kv_free[2 + s], par)) break;        // PV of tile i-2 has run
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&kv_full[2 + s], TILE);
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const long long r = (long long)row0 + lane + 32 * hh;
-                const bool ok = r < p.max_len;
-                const long long off = (long long)j * p.max_len + (ok ? r : 0);
-                cp_async_4(&sm_sc[(s * 2 + 0) * PF_BN + lane + 32 * hh], p.ks + off, ok ? 4u : 0u);
-                cp_async_4(&sm_sc[(s * 2 + 1) * PF_BN + lane + 32 * hh], p.vs + off, ok ? 4u : 0u);
+                    for (int sg = 0; sg < SEGS; ++sg) tma_load_4d(vt + sg * (PF_BN * 128), &tm_v, &kv_full[2 + s], 0, sg, row0, j);
+                }
+                __syncwarp();
+            } else {
+                if (i >= STAGES && !mbar_wait(&kv_free[s], ((i / STAGES) & 1) ^ 1)) break;
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&kv_full[s], 2 * TILE);
+#pragma unroll
+                    for (int sg = 0; sg < SEGS; ++sg) {
+                        tma_load_4d(kt + sg * (PF_BN * 128), &tm_k, &kv_full[s], 0, sg, row0, j);
+                        tma_load_4d(vt + sg * (PF_BN * 128), &tm_v, &kv_full[s], 0, sg, row0, j);
+                    }
+                }
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const long long r = (long long)row0 + lane + 32 * hh;
+                    const bool ok = r < p.max_len;
+                    const long long off = (long long)j * p.max_len + (ok ? r : 0);
+                    cp_async_4(&sm_sc[(s * 2 + 0) * PF_BN + lane + 32 * hh], p.ks + off, ok ? 4u : 0u);
+                    cp_async_4(&sm_sc[(s * 2 + 1) * PF_BN + lane + 32 * hh], p.vs + off, ok ? 4u : 0u);
+                }
+                cp_async_mbar_arrive_noinc(&kv_full[s]);
             }
-            cp_async_mbar_arrive_noinc(&kv_full[s]);
         }
     } else if (warp == 9) {
         // ================================ MMA issuer ==================================
@@ -116,51 +153,84 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         // that QK(i+1) runs while the softmax warps work on tile i.
         const uint32_t q_hi = smem_u32(smem + PF_OFF_Q), q_lo = q_hi + PF_Q_BYTES;
         const uint32_t p_sm = smem_u32(smem + PF_OFF_P);
-        constexpr uint32_t IDESC_QK = umma_idesc_f8(PF_BM, PF_BN, false, false), IDESC_PV = umma_idesc_f8(PF_BM, PF_D, false, true);
+        constexpr uint32_t IDESC_QK = FP8 ? umma_idesc_f8(PF_BM, PF_BN, false, false) : umma_idesc_bf16(PF_BM, PF_BN, false, false);
+        constexpr uint32_t IDESC_PV = FP8 ? umma_idesc_f8(PF_BM, PF_D, false, true) : umma_idesc_bf16(PF_BM, PF_D, false, true);
         auto issue_qk = [&](int i) -> bool {
-            const int s = i % PF_STAGES, b = i & 1;
-            const uint32_t kt = smem_u32(smem + PF_OFF_KV + s * 2 * PF_TILE);
-            if (!mbar_wait(&kv_full[s], (i / PF_STAGES) & 1)) return false;
+            const int s = i % STAGES, b = i & 1;
+            const uint32_t kt = smem_u32(smem + PF_OFF_KV + s * 2 * TILE);
+            PF_TL(i, 8);
+            if (!mbar_wait(&kv_full[s], (i / STAGES) & 1)) return false;
+            PF_TL(i, 9);
             if (i >= 2 && !mbar_wait(&s_free[b], ((i >> 1) & 1) ^ 1)) return false;   // softmax has read S of tile i-2
+            PF_TL(i, 10);
             tc_fence_after();
             if (lane == 0) {
-                // S = Qhi K^T + Qlo K^T : 2 column blocks x 4 k-steps of 32 bytes, hi then lo
+                if constexpr (FP8) {
+                    // S = Qhi K^T + Qlo K^T : 2 column blocks x 4 k-steps of 32 bytes, hi then lo
 #pragma unroll
-                for (int term = 0; term < 2; ++term)
+                    for (int term = 0; term < 2; ++term)
 #pragma unroll
-                    for (int sg = 0; sg < 2; ++sg)
+                        for (int sg = 0; sg < 2; ++sg)
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const uint64_t a = umma_desc((term ? q_lo : q_hi) + sg * (PF_BM * 128) + k * 32, 16, 1024);
+                                const uint64_t bd = umma_desc(kt + sg * (PF_BN * 128) + k * 32, 16, 1024);
+                                tc_mma_f8(tmem + PF_TMEM_S + b * PF_BN, a, bd, IDESC_QK, (term | sg | k) ? 1u : 0u);
+                            }
+                } else {
+                    // S = Q K^T : 4 column blocks of 64 dims x 4 k-steps of 16 dims (32 bytes)
+#pragma unroll
+                    for (int sg = 0; sg < 4; ++sg)
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const uint64_t a = umma_desc((term ? q_lo : q_hi) + sg * (PF_BM * 128) + k * 32, 16, 1024);
+                            const uint64_t a = umma_desc(q_hi + sg * (PF_BM * 128) + k * 32, 16, 1024);
                             const uint64_t bd = umma_desc(kt + sg * (PF_BN * 128) + k * 32, 16, 1024);
-                            tc_mma_f8(tmem + PF_TMEM_S + b * PF_BN, a, bd, IDESC_QK, (term | sg | k) ? 1u : 0u);
+                            tc_mma_bf16(tmem + PF_TMEM_S + b * PF_BN, a, bd, IDESC_QK, (sg | k) ? 1u : 0u);
                         }
+                    tc_commit(&kv_free[s]);                                          // the K tile may be refilled
+                }
                 tc_commit(&s_full[b]);
             }
+            PF_TL(i, 11);
             __syncwarp();
             return true;
         };
         bool ok = mbar_wait(q_ready, 0);                                      // query block staged
         if (ok && n_tiles > 0) ok = issue_qk(0);
         for (int i = 0; i < n_tiles && ok; ++i) {
-            const int s = i % PF_STAGES;
-            const uint32_t vt = smem_u32(smem + PF_OFF_KV + s * 2 * PF_TILE) + PF_TILE;
+            const int s = i % STAGES;
+            const uint32_t vt = smem_u32(smem + PF_OFF_KV + s * 2 * TILE) + TILE;
             if (i + 1 < n_tiles && !(ok = issue_qk(i + 1))) break;
+            PF_TL(i, 12);
+            if constexpr (!FP8) { if (!(ok = mbar_wait(&kv_full[2 + s], (i / STAGES) & 1))) break; }   // V tile landed
+            PF_TL(i, 13);
             if (!(ok = mbar_wait(p_full, i & 1))) break;                        // P of tile i staged (and O corrected)
+            PF_TL(i, 14);
             tc_fence_after();
             if (lane == 0) {
-                // O += Phi V + Plo V : P row = [hi 64 B | lo 64 B]; V tile MN-major, 32 keys per step
+                if constexpr (FP8) {
+                    // O += Phi V + Plo V : P row = [hi 64 B | lo 64 B]; V tile MN-major, 32 keys per step
 #pragma unroll
-                for (int term = 0; term < 2; ++term)
+                    for (int term = 0; term < 2; ++term)
 #pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        const uint64_t a = umma_desc(p_sm + term * 64 + k * 32, 16, 1024);
-                        const uint64_t bd = umma_desc(vt + k * (32 * 128), PF_BN * 128, 1024);
-                        tc_mma_f8(tmem + PF_TMEM_O, a, bd, IDESC_PV, (i | term | k) ? 1u : 0u);
+                        for (int k = 0; k < 2; ++k) {
+                            const uint64_t a = umma_desc(p_sm + term * 64 + k * 32, 16, 1024);
+                            const uint64_t bd = umma_desc(vt + k * (32 * 128), PF_BN * 128, 1024);
+                            tc_mma_f8(tmem + PF_TMEM_O, a, bd, IDESC_PV, (i | term | k) ? 1u : 0u);
+                        }
+                } else {
+                    // O += P V : P row = 64 keys x 2 bytes; V tile MN-major (four 64-dim column blocks), 16 keys per step
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t a = umma_desc(p_sm + k * 32, 16, 1024);
+                        const uint64_t bd = umma_desc(vt + k * (16 * 128), PF_BN * 128, 1024);
+                        tc_mma_bf16(tmem + PF_TMEM_O, a, bd, IDESC_PV, (i | k) ? 1u : 0u);
                     }
-                tc_commit(&kv_free[s]);
+                }
+                tc_commit(&kv_free[FP8 ? s : 2 + s]);
                 tc_commit(o_done);
             }
+            PF_TL(i, 15);
             __syncwarp();
         }
     } else {
@@ -174,7 +244,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         // ---- stage the query block as two e4m3 copies (power-of-two row scale, hi + lo): both
         // threads of a row find the row maximum, each converts its 128 dims
         float qinv = 1.f;
-        {
+        if constexpr (!FP8) {
+            // bf16: the query rows as they are, four column blocks of 64 dims; rows past t are zero
+            const __nv_bfloat16 *qp = p.q + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D;
+#pragma unroll 4
+            for (int cc = 0; cc < PF_D / 16; ++cc) {                           // this thread's 16 chunks of 8 dims
+                const int c = half * (PF_D / 16) + cc;
+                const uint4 raw = row_ok ? *reinterpret_cast<const uint4 *>(qp + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4 *>(smem + PF_OFF_Q + (c >> 3) * (PF_BM * 128) + sw128(row, (c & 7) * 16)) = raw;
+            }
+        } else {
             const __nv_bfloat16 *qp = p.q + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D;
             float amax = 0.f;
             for (int c = 0; c < PF_D / 8; ++c) {
@@ -212,7 +291,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         bool ok = true;
         const long long qpos_warp_min = p.pos + q0 + (warp & 3) * 32;            // lane 0's position
         const bool warp_has_padding = (warp & 3) * 32 + 31 >= rows_here;
-        if (n_tiles > 0) {
+        if (FP8 && n_tiles > 0) {
             ok = mbar_wait(&kv_full[0], 0);
             if (ok && tid < PF_BN) {
                 const float kscv = sm_sc[tid], vscv = sm_sc[PF_BN + tid];
@@ -228,7 +307,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             // ahead: the table of tile i+1 is written here and published by this tile's barrier below
             float *fac = sm_fac + (i % 3) * 3 * PF_BN;
             float *mxbuf = sm_mx + b * 2 * PF_BM;
-            if (i + 1 < n_tiles) {
+            if (FP8 && i + 1 < n_tiles) {
                 const int s1 = (i + 1) % PF_STAGES;
                 if (!(ok = mbar_wait(&kv_full[s1], ((i + 1) / PF_STAGES) & 1))) break;
                 if (tid < PF_BN) {
@@ -239,16 +318,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                     fn[2 * PF_BN + tid] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
                 }
             }
+            PF_TL(i, 0);
             if (!(ok = mbar_wait(&s_full[b], (i >> 1) & 1))) break;
+            PF_TL(i, 1);
             tc_fence_after();
             float sv[32];
             tmem_ld32(lane_addr + PF_TMEM_S + b * PF_BN + half * 32, sv);
+            PF_TL(i, 2);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_free[b]);                             // this S buffer may be overwritten by tile i+2
             // scores -> exponent domain (t = raw * k_scale * c * q_inv + log2 v_scale), row maximum
             const long long key0 = (long long)i * PF_BN + half * 32;
             const float *fa_ = fac + half * 32, *fb_ = fac + PF_BN + half * 32, *fr_ = fac + 2 * PF_BN + half * 32;
+            if constexpr (!FP8) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) sv[c] *= p.scale_log2;
+            } else
 #pragma unroll
             for (int c4 = 0; c4 < 8; ++c4) {
                 const float4 fa = *reinterpret_cast<const float4 *>(fa_ + c4 * 4);
@@ -267,14 +353,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
             for (int c = 0; c < 32; ++c) mt = fmaxf(mt, sv[c]);
             mxbuf[half * PF_BM + row] = mt;
+            PF_TL(i, 3);
             named_barrier(1, PF_SOFTMAX_THREADS);
+            PF_TL(i, 4);
             mt = fmaxf(mt, mxbuf[(half ^ 1) * PF_BM + row]);
             const float m_new = fmaxf(m_run, mt);
             const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-            const float m_off = m_safe - 8.f;                                   // probabilities are staged x 256
+            const float m_off = FP8 ? m_safe - 8.f : m_safe;                    // e4m3 probabilities are staged x 256
             const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run - m_safe);   // rows with no visible key yet
             // the previous PV must have landed before P is overwritten or O is corrected
             if (i > 0 && !(ok = mbar_wait(o_done, (i - 1) & 1))) break;
+            PF_TL(i, 5);
             tc_fence_after();
             if (__any_sync(0xffffffffu, alpha != 1.f) && i > 0) {               // this thread corrects its 128 columns
 #pragma unroll 1
@@ -287,6 +376,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                 }
             }
             float lsum = 0.f;
+            if constexpr (!FP8) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {                                   // 8 keys -> one 16-byte chunk of bf16
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = fast_exp2(sv[c * 8 + e * 2] - m_off), p1 = fast_exp2(sv[c * 8 + e * 2 + 1] - m_off);
+                        lsum += p0 + p1;
+                        w[e] = pack_bf16x2(p0, p1);
+                    }
+                    *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, half * 64 + c * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            } else
 #pragma unroll
             for (int c = 0; c < 2; ++c) {                                       // 16 keys -> one chunk of hi and of lo codes
                 uint32_t hw[4], lw[4];
@@ -307,12 +409,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             }
             l_run = fmaf(l_run, alpha, lsum);
             m_run = m_new;
+            PF_TL(i, 6);
             fence_async_smem();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
+            PF_TL(i, 7);
         }
-        // ---- epilogue: O / l -> bf16 (both carry the factor 256); l = sum of the two halves' partial sums
+        // ---- epilogue: O / l -> bf16 (with e4m3 both carry the factor 256); l = sum of the two halves' partial sums
         if (ok && n_tiles > 0) ok = mbar_wait(o_done, (n_tiles - 1) & 1);
         tc_fence_after();
         sm_mx[half * PF_BM + row] = l_run;
@@ -354,7 +458,7 @@ extern "C" int trb_attn_prefill(const trb_cache_t *cache, const void *q, void *o
     int rc = make_cache_view(cache, &c);
     if (rc) return rc;
     if (!q || !out || t < 1 || hq < 1 || hq % c.hkv || pos < 0) return TRB_E_ARG;
-    if (!c.fp8 || c.d != PF_D || c.ring > 0 || c.sharded) return TRB_E_UNSUPPORTED;
+    if (c.d != PF_D || c.ring > 0 || c.sharded) return TRB_E_UNSUPPORTED;
     if (pos + t > c.max_len) return TRB_E_CAPACITY;
     if (((uintptr_t)q | (uintptr_t)out) & 15) return TRB_E_ALIGN;
     if (c.max_len >= (1LL << 31) - 64) return TRB_E_UNSUPPORTED;
@@ -363,18 +467,21 @@ extern "C" int trb_attn_prefill(const trb_cache_t *cache, const void *q, void *o
     p.t = t; p.hq = hq; p.hkv = c.hkv; p.g = hq / c.hkv; p.pos = pos; p.max_len = c.max_len;
     p.scale_log2 = scale * 1.4426950408889634f;
     CUtensorMap mk, mv;
-    if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, PF_D, PF_BN, &mk))) return rc;
-    if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, PF_D, PF_BN, &mv))) return rc;
+    const int row_bytes = PF_D * (c.fp8 ? 1 : 2);
+    if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, row_bytes, PF_BN, &mk))) return rc;
+    if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, row_bytes, PF_BN, &mv))) return rc;
     static bool attr_set[64] = {};
     int dev = 0;
     TRB_CUDA_CHECK(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        TRB_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
+        TRB_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
+        TRB_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
         attr_set[dev & 63] = true;
     }
     dim3 grid((t + PF_BM - 1) / PF_BM, hq);
     pdl_note_fence((cudaStream_t)stream);
-    prefill_kernel<<<grid, PF_THREADS, PF_SMEM, (cudaStream_t)stream>>>(mk, mv, p);
+    if (c.fp8) prefill_kernel<true><<<grid, PF_THREADS, PF_SMEM, (cudaStream_t)stream>>>(mk, mv, p);
+    else prefill_kernel<false><<<grid, PF_THREADS, PF_SMEM, (cudaStream_t)stream>>>(mk, mv, p);
     TRB_CUDA_CHECK(cudaGetLastError());
     return TRB_OK;
 }

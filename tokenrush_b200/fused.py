@@ -263,10 +263,10 @@ def attn_prefill_fused(q, k_cache, v_cache, pos, cfg, k_scale=None, v_scale=None
     if q.dtype != torch.bfloat16 or not q.is_contiguous():
         raise ValueError("q must be contiguous bf16 [T, HQ, D]")
     cache = _cache(k_cache, v_cache, k_scale, v_scale)
-    if k_cache.dtype == torch.bfloat16:
-        # The tensor-core prefill kernel reads the fp8 cache only.  A bf16 cache (the reference's default,
-        # tokenrush/fused.py:523-533 with FP8 = False) goes through the M-row decode kernel, whose bf16
-        # path reads the cache with ldmatrix, in groups of as many rows as one launch takes.
+    if k_cache.dtype == torch.bfloat16 and D != 256:
+        # The tensor-core prefill kernel is built for 256-dim heads (e4m3 or bf16 cache; the reference's
+        # default is bf16, tokenrush/fused.py:523-533 with FP8 = False).  A bf16 cache of another head
+        # size goes through the M-row decode kernel, in groups of as many rows as one launch takes.
         HKV = k_cache.shape[0]
         m_max = max(1, 48 // (HQ // HKV))
         o = torch.empty_like(q)
