@@ -1,16 +1,23 @@
-// Chunked prefill attention over the FP8 KV cache on the 5th-generation tensor cores
-// (tcgen05.mma, accumulators in tensor memory).
+// Chunked prefill attention over the KV cache (e4m3 + scales, or bf16) on the 5th-generation
+// tensor cores (tcgen05.mma, accumulators and the A operands in tensor memory).
 //
-// One CTA per (128-query block, query head).  Keys stream in tiles of 64 through a 4-stage TMA
-// ring; per tile
+// One CTA per (128-query block, query head).  Keys stream in tiles of 64 through a TMA ring; per tile
 //     S[128 x 64]   = (Qhi + Qlo) K^T         tcgen05.mma kind::f8f6f4, K straight from the TMA tile
-//     P             = exp2(S * k_scale * c + log2 v_scale - m)     128 threads, one query row each
+//     P             = exp2(S * k_scale * c + log2 v_scale - m)     256 threads, (query row, key half) each
 //     O[128 x 256] += (Phi + Plo) V           tcgen05.mma, V as an MN-major operand, same tile
 // The e4m3 codes of the cache feed the tensor cores unconverted.  The bf16 queries and the fp32
 // probabilities are each split into two e4m3 terms (x ~= hi + lo: 8 significant bits, what bf16
 // carries), so every product is exact and accumulation is fp32 in tensor memory; at the FP8 rate
 // the two terms cost what one bf16 pass would.  Per-key scales never touch the codes: the K scale
 // multiplies the fp32 score, the V scale is moved into the exponent of the probability.
+// Over a bf16 cache the same kernel issues kind::f16 MMAs on the bf16 rows as they are.
+//
+// Both A operands live in tensor memory: the query block is written there once (tcgen05.st by the
+// thread that owns the row), and the probabilities of a tile are written over the scores they
+// came from.  An MMA that takes A from shared memory re-reads the whole query block (64 KB) for
+// every key tile, which alone is more than the shared-memory bandwidth of the time the tile's
+// math takes; with A in tensor memory only the K and V tiles cross shared memory (64 KB per tile),
+// and the freed 80 KB hold more pipeline stages.
 //
 // Warp roles: warps 0-7 softmax / correction / epilogue (two warpgroups; thread = one query row
 // = one TMEM lane, and one half of the tile's keys / of the output columns), warp 8 TMA
@@ -24,23 +31,20 @@ namespace trb {
 
 constexpr int PF_BM = 128;              // queries per CTA
 constexpr int PF_BN = 64;               // keys per tile
-constexpr int PF_D = 256;               // head dim (bytes per e4m3 row)
-constexpr int PF_STAGES = 4;
+constexpr int PF_D = 256;               // head dim
+constexpr int PF_MAXST = 6;             // pipeline stages: 6 of (16 KB K, 16 KB V) for e4m3, 3 of (32 KB, 32 KB) for bf16
 constexpr int PF_SOFTMAX_THREADS = 256;     // two warpgroups: thread = (query row, half of the tile's keys)
 constexpr int PF_THREADS = PF_SOFTMAX_THREADS + 64;   // + TMA warp + MMA warp
-constexpr int PF_TILE = PF_BN * PF_D;   // bytes of one K or V tile
-constexpr int PF_Q_BYTES = PF_BM * PF_D;               // one e4m3 copy of the query block
-constexpr int PF_P_BYTES = PF_BM * 128;                // [128 rows][hi 64 B | lo 64 B]
-constexpr int PF_OFF_Q = 0;                            // Qhi, Qlo
-constexpr int PF_OFF_KV = 2 * PF_Q_BYTES;              // stages of (K tile, V tile)
-constexpr int PF_OFF_P = PF_OFF_KV + PF_STAGES * 2 * PF_TILE;
-constexpr int PF_OFF_SC = PF_OFF_P + PF_P_BYTES;       // [stages][2][64] floats
-constexpr int PF_OFF_FAC = PF_OFF_SC + PF_STAGES * 2 * PF_BN * 4;   // [3][3][64] floats: per-key factors of a tile, tiles i-1, i, i+1
+constexpr int PF_KV_BYTES = 192 * 1024;
+constexpr int PF_OFF_KV = 0;                           // stages of (K tile, V tile)
+constexpr int PF_OFF_SC = PF_OFF_KV + PF_KV_BYTES;     // [stages][2][64] floats
+constexpr int PF_OFF_FAC = PF_OFF_SC + PF_MAXST * 2 * PF_BN * 4;   // [3][3][64] floats: per-key factors of a tile, tiles i-1, i, i+1
 constexpr int PF_OFF_MX = PF_OFF_FAC + 3 * 3 * PF_BN * 4;          // [2][2][128] floats: row maxima of the two key halves
 constexpr int PF_OFF_BAR = PF_OFF_MX + 2 * 2 * PF_BM * 4;
 constexpr int PF_SMEM = PF_OFF_BAR + 256 + 1024;
 constexpr int PF_TMEM_COLS = 512;
-constexpr int PF_TMEM_S = 0;            // S: two buffers, columns [0, 64) and [64, 128)
+constexpr int PF_TMEM_S = 0;            // S: two buffers, columns [0, 64) and [64, 128); P of a tile over the first 32 columns of its S
+constexpr int PF_TMEM_Q = 128;          // the query block: bf16 [128, 256), or e4m3 hi [128, 192) and lo [192, 256)
 constexpr int PF_TMEM_O = 256;          // O: columns [256, 512)
 
 struct PrefillParams {
@@ -53,9 +57,10 @@ struct PrefillParams {
 };
 
 // FP8 = false: the same kernel over a bf16 cache (the reference's default mode, tokenrush/fused.py:523-533
-// with FP8 = False): K, V and Q feed tcgen05.mma kind::f16 as bf16 straight from the TMA tiles and
-// the staged query rows, the probabilities are staged as bf16; no scales, no hi + lo terms.  Rows are
-// 512 bytes (four 128-byte column blocks), tiles 32 KB, so two pipeline stages take the place of four.
+// with FP8 = False): K, V and Q feed tcgen05.mma kind::f16 as bf16 as they are, the probabilities
+// are written as bf16; no scales, no hi + lo terms.  Rows are 512 bytes (four 128-byte column
+// blocks), tiles 32 KB, three stages; K and V tiles have barriers of their own, so that a K tile is
+// refilled as soon as its QK^T has run.
 // Diagnostic build only: the last query block of head 0 stamps clock64 at fixed points of tiles 64..95
 // (slots 0-7: lane 0 of softmax warp 0, slots 8-15: lane 0 of the MMA warp) into timeline launch slot 63.
 #ifdef TRB_TIMELINE
@@ -67,17 +72,18 @@ struct PrefillParams {
 template <bool FP8>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
-    constexpr int ROWB = PF_D * (FP8 ? 1 : 2), SEGS = ROWB / 128, TILE = PF_BN * ROWB, STAGES = FP8 ? PF_STAGES : PF_STAGES / 2;
-    static_assert(STAGES * 2 * TILE == PF_STAGES * 2 * PF_TILE && (FP8 ? 2 : 1) * PF_BM * ROWB == 2 * PF_Q_BYTES, "shared-memory layout");
+    constexpr int ROWB = PF_D * (FP8 ? 1 : 2), SEGS = ROWB / 128, TILE = PF_BN * ROWB, STAGES = FP8 ? PF_MAXST : PF_MAXST / 2;
+    constexpr int VB = FP8 ? 0 : PF_MAXST / 2;          // barrier index of a stage's V tile relative to its K tile
+    static_assert(STAGES * 2 * TILE == PF_KV_BYTES, "shared-memory layout");
     extern __shared__ uint8_t pf_smem_raw[];
     uint8_t *smem = pf_smem_raw + ((1024u - (smem_u32(pf_smem_raw) & 1023u)) & 1023u);
     float *sm_sc = reinterpret_cast<float *>(smem + PF_OFF_SC);
     float *sm_fac = reinterpret_cast<float *>(smem + PF_OFF_FAC);
     float *sm_mx = reinterpret_cast<float *>(smem + PF_OFF_MX);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + PF_OFF_BAR);
-    uint64_t *kv_full = bars, *kv_free = bars + PF_STAGES;   // (STAGES of each are used)
-    uint64_t *s_full = bars + 2 * PF_STAGES, *s_free = s_full + 2, *p_full = s_full + 4, *o_done = s_full + 5, *q_ready = s_full + 6;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_full + 7);
+    uint64_t *kv_full = bars, *kv_free = bars + PF_MAXST;
+    uint64_t *s_full = bars + 2 * PF_MAXST, *p_full = s_full + 2, *o_done = s_full + 3, *q_ready = s_full + 4;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_full + 5);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = blockIdx.x, h = blockIdx.y, j = h / p.g;
@@ -91,10 +97,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #endif
 
     if (threadIdx.x == 0) {
-        // FP8: one barrier pair per stage (K + V tile + 64 scale pairs).  bf16: the two stages' K tiles on
-        // barriers 0-1 and V tiles on 2-3, so that a K tile is refilled as soon as its QK^T has run
-        for (int s = 0; s < PF_STAGES; ++s) { mbar_init(&kv_full[s], FP8 ? 33u : 1u); mbar_init(&kv_free[s], 1u); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1u); mbar_init(&s_free[b], 8u); }
+        // FP8: one barrier pair per stage (K + V tile + 64 scale pairs).  bf16: the stages' K tiles on
+        // barriers 0-2 and their V tiles on 3-5
+        for (int s = 0; s < PF_MAXST; ++s) { mbar_init(&kv_full[s], FP8 ? 33u : 1u); mbar_init(&kv_free[s], 1u); }
+        for (int b = 0; b < 2; ++b) mbar_init(&s_full[b], 1u);
         mbar_init(p_full, 8u); mbar_init(o_done, 1u); mbar_init(q_ready, 8u);
         mbar_fence_init();
         tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
@@ -113,17 +119,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             uint8_t *kt = smem + PF_OFF_KV + s * 2 * TILE, *vt = kt + TILE;
             if constexpr (!FP8) {
                 const uint32_t par = ((i / STAGES) & 1) ^ 1;
-                if (i >= STAGES && !mbar_wait(&kv_free[s], par)) break;            // QK^T of tile i-2 has run
+                if (i >= STAGES && !mbar_wait(&kv_free[s], par)) break;            // QK^T of tile i-3 has run
                 if (lane == 0) {
                     mbar_arrive_expect_tx(&kv_full[s], TILE);
 #pragma unroll
                     for (int sg = 0; sg < SEGS; ++sg) tma_load_4d(kt + sg * (PF_BN * 128), &tm_k, &kv_full[s], 0, sg, row0, j);
                 }
-                if (i >= STAGES && !mbar_wait(&kv_free[2 + s], par)) break;        // PV of tile i-2 has run
+                if (i >= STAGES && !mbar_wait(&kv_free[VB + s], par)) break;       // PV of tile i-3 has run
                 if (lane == 0) {
-                    mbar_arrive_expect_tx(&kv_full[2 + s], TILE);
+                    mbar_arrive_expect_tx(&kv_full[VB + s], TILE);
 #pragma unroll
-                    for (int sg = 0; sg < SEGS; ++sg) tma_load_4d(vt + sg * (PF_BN * 128), &tm_v, &kv_full[2 + s], 0, sg, row0, j);
+                    for (int sg = 0; sg < SEGS; ++sg) tma_load_4d(vt + sg * (PF_BN * 128), &tm_v, &kv_full[VB + s], 0, sg, row0, j);
                 }
                 __syncwarp();
             } else {
@@ -150,9 +156,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     } else if (warp == 9) {
         // ================================ MMA issuer ==================================
         // order on the tensor pipe: QK(0), QK(1), PV(0), QK(2), PV(1), ...  S is double-buffered so
-        // that QK(i+1) runs while the softmax warps work on tile i.
-        const uint32_t q_hi = smem_u32(smem + PF_OFF_Q), q_lo = q_hi + PF_Q_BYTES;
-        const uint32_t p_sm = smem_u32(smem + PF_OFF_P);
+        // that QK(i+1) runs while the softmax warps work on tile i.  The pipe runs in order of issue:
+        // QK(i+2) overwrites the S buffer whose first columns hold P(i) only after PV(i) has read them.
+        const uint32_t q_hi = tmem + PF_TMEM_Q, q_lo = q_hi + 64;
         constexpr uint32_t IDESC_QK = FP8 ? umma_idesc_f8(PF_BM, PF_BN, false, false) : umma_idesc_bf16(PF_BM, PF_BN, false, false);
         constexpr uint32_t IDESC_PV = FP8 ? umma_idesc_f8(PF_BM, PF_D, false, true) : umma_idesc_bf16(PF_BM, PF_D, false, true);
         auto issue_qk = [&](int i) -> bool {
@@ -161,31 +167,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             PF_TL(i, 8);
             if (!mbar_wait(&kv_full[s], (i / STAGES) & 1)) return false;
             PF_TL(i, 9);
-            if (i >= 2 && !mbar_wait(&s_free[b], ((i >> 1) & 1) ^ 1)) return false;   // softmax has read S of tile i-2
             PF_TL(i, 10);
             tc_fence_after();
             if (lane == 0) {
                 if constexpr (FP8) {
-                    // S = Qhi K^T + Qlo K^T : 2 column blocks x 4 k-steps of 32 bytes, hi then lo
+                    // S = Qhi K^T + Qlo K^T : 2 column blocks x 4 k-steps of 32 dims (8 TMEM columns of Q), hi then lo
 #pragma unroll
                     for (int term = 0; term < 2; ++term)
 #pragma unroll
                         for (int sg = 0; sg < 2; ++sg)
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
-                                const uint64_t a = umma_desc((term ? q_lo : q_hi) + sg * (PF_BM * 128) + k * 32, 16, 1024);
                                 const uint64_t bd = umma_desc(kt + sg * (PF_BN * 128) + k * 32, 16, 1024);
-                                tc_mma_f8(tmem + PF_TMEM_S + b * PF_BN, a, bd, IDESC_QK, (term | sg | k) ? 1u : 0u);
+                                tc_mma_f8_ts(tmem + PF_TMEM_S + b * PF_BN, (term ? q_lo : q_hi) + (sg * 4 + k) * 8, bd, IDESC_QK, (term | sg | k) ? 1u : 0u);
                             }
                 } else {
-                    // S = Q K^T : 4 column blocks of 64 dims x 4 k-steps of 16 dims (32 bytes)
+                    // S = Q K^T : 4 column blocks of 64 dims x 4 k-steps of 16 dims (8 TMEM columns of Q)
 #pragma unroll
                     for (int sg = 0; sg < 4; ++sg)
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const uint64_t a = umma_desc(q_hi + sg * (PF_BM * 128) + k * 32, 16, 1024);
                             const uint64_t bd = umma_desc(kt + sg * (PF_BN * 128) + k * 32, 16, 1024);
-                            tc_mma_bf16(tmem + PF_TMEM_S + b * PF_BN, a, bd, IDESC_QK, (sg | k) ? 1u : 0u);
+                            tc_mma_bf16_ts(tmem + PF_TMEM_S + b * PF_BN, q_hi + (sg * 4 + k) * 8, bd, IDESC_QK, (sg | k) ? 1u : 0u);
                         }
                     tc_commit(&kv_free[s]);                                          // the K tile may be refilled
                 }
@@ -200,34 +203,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int s = i % STAGES;
             const uint32_t vt = smem_u32(smem + PF_OFF_KV + s * 2 * TILE) + TILE;
+            const uint32_t p_tm = tmem + PF_TMEM_S + (i & 1) * PF_BN;                // P(i) lies over the first columns of S(i)
             if (i + 1 < n_tiles && !(ok = issue_qk(i + 1))) break;
             PF_TL(i, 12);
-            if constexpr (!FP8) { if (!(ok = mbar_wait(&kv_full[2 + s], (i / STAGES) & 1))) break; }   // V tile landed
+            if constexpr (!FP8) { if (!(ok = mbar_wait(&kv_full[VB + s], (i / STAGES) & 1))) break; }   // V tile landed
             PF_TL(i, 13);
             if (!(ok = mbar_wait(p_full, i & 1))) break;                        // P of tile i staged (and O corrected)
             PF_TL(i, 14);
             tc_fence_after();
             if (lane == 0) {
                 if constexpr (FP8) {
-                    // O += Phi V + Plo V : P row = [hi 64 B | lo 64 B]; V tile MN-major, 32 keys per step
+                    // O += Phi V + Plo V : P row = hi codes in columns [0, 16), lo in [16, 32); V tile MN-major, 32 keys per step
 #pragma unroll
                     for (int term = 0; term < 2; ++term)
 #pragma unroll
                         for (int k = 0; k < 2; ++k) {
-                            const uint64_t a = umma_desc(p_sm + term * 64 + k * 32, 16, 1024);
                             const uint64_t bd = umma_desc(vt + k * (32 * 128), PF_BN * 128, 1024);
-                            tc_mma_f8(tmem + PF_TMEM_O, a, bd, IDESC_PV, (i | term | k) ? 1u : 0u);
+                            tc_mma_f8_ts(tmem + PF_TMEM_O, p_tm + term * 16 + k * 8, bd, IDESC_PV, (i | term | k) ? 1u : 0u);
                         }
                 } else {
-                    // O += P V : P row = 64 keys x 2 bytes; V tile MN-major (four 64-dim column blocks), 16 keys per step
+                    // O += P V : P row = 64 keys in 32 columns; V tile MN-major (four 64-dim column blocks), 16 keys per step
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const uint64_t a = umma_desc(p_sm + k * 32, 16, 1024);
                         const uint64_t bd = umma_desc(vt + k * (16 * 128), PF_BN * 128, 1024);
-                        tc_mma_bf16(tmem + PF_TMEM_O, a, bd, IDESC_PV, (i | k) ? 1u : 0u);
+                        tc_mma_bf16_ts(tmem + PF_TMEM_O, p_tm + k * 8, bd, IDESC_PV, (i | k) ? 1u : 0u);
                     }
                 }
-                tc_commit(&kv_free[FP8 ? s : 2 + s]);
+                tc_commit(&kv_free[VB + s]);
                 tc_commit(o_done);
             }
             PF_TL(i, 15);
@@ -245,14 +247,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         // threads of a row find the row maximum, each converts its 128 dims
         float qinv = 1.f;
         if constexpr (!FP8) {
-            // bf16: the query rows as they are, four column blocks of 64 dims; rows past t are zero
-            const __nv_bfloat16 *qp = p.q + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D;
-#pragma unroll 4
-            for (int cc = 0; cc < PF_D / 16; ++cc) {                           // this thread's 16 chunks of 8 dims
-                const int c = half * (PF_D / 16) + cc;
-                const uint4 raw = row_ok ? *reinterpret_cast<const uint4 *>(qp + c * 8) : make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4 *>(smem + PF_OFF_Q + (c >> 3) * (PF_BM * 128) + sw128(row, (c & 7) * 16)) = raw;
+            // bf16: the query rows as they are, two dims per TMEM column; this thread's 128 dims = 64 columns;
+            // rows past t are zero
+            const __nv_bfloat16 *qp = p.q + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D + half * (PF_D / 2);
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                uint32_t w[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 raw = row_ok ? *reinterpret_cast<const uint4 *>(qp + blk * 64 + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+                    w[c * 4 + 0] = raw.x; w[c * 4 + 1] = raw.y; w[c * 4 + 2] = raw.z; w[c * 4 + 3] = raw.w;
+                }
+                tmem_st32_raw(lane_addr + PF_TMEM_Q + half * 64 + blk * 32, w);
             }
+            tmem_st_wait();
         } else {
             const __nv_bfloat16 *qp = p.q + ((long long)(q0 + (row_ok ? row : 0)) * p.hq + h) * PF_D;
             float amax = 0.f;
@@ -267,23 +275,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             if (e > 90) e = 90;
             const float sc = row_ok ? __uint_as_float((uint32_t)(127 + 7 - e) << 23) : 0.f;
             qinv = __uint_as_float((uint32_t)(127 - 7 + e) << 23);
-            for (int cc = 0; cc < PF_D / 32; ++cc) {                           // this thread's 8 chunks of 16 dims
-                const int c = half * (PF_D / 32) + cc;
-                uint32_t hw[4], lw[4];
+            uint32_t hw[32], lw[32];                                           // this thread's 128 dims: 32 columns of hi and of lo codes
 #pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const uint2 raw = *reinterpret_cast<const uint2 *>(qp + c * 16 + w * 4);
-                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
-                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
-                    const float y[4] = {a.x * sc, a.y * sc, b.x * sc, b.y * sc};
-                    pf_split4(y, hw[w], lw[w]);
-                }
-                const uint32_t off = (c >> 3) * (PF_BM * 128) + sw128(row, (c & 7) * 16);
-                *reinterpret_cast<uint4 *>(smem + PF_OFF_Q + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                *reinterpret_cast<uint4 *>(smem + PF_OFF_Q + PF_Q_BYTES + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+            for (int w = 0; w < 32; ++w) {
+                const uint2 raw = *reinterpret_cast<const uint2 *>(qp + half * (PF_D / 2) + w * 4);
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+                const float y[4] = {a.x * sc, a.y * sc, b.x * sc, b.y * sc};
+                pf_split4(y, hw[w], lw[w]);
             }
+            tmem_st32_raw(lane_addr + PF_TMEM_Q + half * 32, hw);
+            tmem_st32_raw(lane_addr + PF_TMEM_Q + 64 + half * 32, lw);
+            tmem_st_wait();
         }
-        fence_async_smem();
+        tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(q_ready);
 
@@ -308,8 +313,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             float *fac = sm_fac + (i % 3) * 3 * PF_BN;
             float *mxbuf = sm_mx + b * 2 * PF_BM;
             if (FP8 && i + 1 < n_tiles) {
-                const int s1 = (i + 1) % PF_STAGES;
-                if (!(ok = mbar_wait(&kv_full[s1], ((i + 1) / PF_STAGES) & 1))) break;
+                const int s1 = (i + 1) % STAGES;
+                if (!(ok = mbar_wait(&kv_full[s1], ((i + 1) / STAGES) & 1))) break;
                 if (tid < PF_BN) {
                     float *fn = sm_fac + ((i + 1) % 3) * 3 * PF_BN;
                     const float kscv = sm_sc[(s1 * 2 + 0) * PF_BN + tid], vscv = sm_sc[(s1 * 2 + 1) * PF_BN + tid];
@@ -325,9 +330,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             float sv[32];
             tmem_ld32(lane_addr + PF_TMEM_S + b * PF_BN + half * 32, sv);
             PF_TL(i, 2);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_free[b]);                             // this S buffer may be overwritten by tile i+2
             // scores -> exponent domain (t = raw * k_scale * c * q_inv + log2 v_scale), row maximum
             const long long key0 = (long long)i * PF_BN + half * 32;
             const float *fa_ = fac + half * 32, *fb_ = fac + PF_BN + half * 32, *fr_ = fac + 2 * PF_BN + half * 32;
@@ -361,11 +363,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             const float m_safe = m_new == -INFINITY ? 0.f : m_new;
             const float m_off = FP8 ? m_safe - 8.f : m_safe;                    // e4m3 probabilities are staged x 256
             const float alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run - m_safe);   // rows with no visible key yet
-            // the previous PV must have landed before P is overwritten or O is corrected
-            if (i > 0 && !(ok = mbar_wait(o_done, (i - 1) & 1))) break;
-            PF_TL(i, 5);
-            tc_fence_after();
+            // O is corrected only where a row maximum of this warp moved, and only then the previous PV must
+            // have landed (S of this tile exists, so PV(i-2) has completed: the parity cannot be mistaken)
             if (__any_sync(0xffffffffu, alpha != 1.f) && i > 0) {               // this thread corrects its 128 columns
+                if (!(ok = mbar_wait(o_done, (i - 1) & 1))) break;
+                tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < PF_D / 64; ++c) {
                     float ov[32];
@@ -375,20 +377,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                     tmem_st32(lane_addr + PF_TMEM_O + half * (PF_D / 2) + c * 32, ov);
                 }
             }
+            PF_TL(i, 5);
+            const uint32_t p_tm = lane_addr + PF_TMEM_S + b * PF_BN;            // P over the first columns of this tile's S (all of S was read before the barrier above)
             float lsum = 0.f;
             if constexpr (!FP8) {
+                uint32_t w[16];                                                 // this thread's 32 keys, two per column
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {                                   // 8 keys -> one 16-byte chunk of bf16
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float p0 = fast_exp2(sv[c * 8 + e * 2] - m_off), p1 = fast_exp2(sv[c * 8 + e * 2 + 1] - m_off);
-                        lsum += p0 + p1;
-                        w[e] = pack_bf16x2(p0, p1);
-                    }
-                    *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, half * 64 + c * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int e = 0; e < 16; ++e) {
+                    const float p0 = fast_exp2(sv[e * 2] - m_off), p1 = fast_exp2(sv[e * 2 + 1] - m_off);
+                    lsum += p0 + p1;
+                    w[e] = pack_bf16x2(p0, p1);
                 }
-            } else
+                tmem_st16_raw(p_tm + half * 16, w);
+            } else {
+            uint32_t hw8[8], lw8[8];                                            // this thread's 32 keys: 8 columns of hi and of lo codes
 #pragma unroll
             for (int c = 0; c < 2; ++c) {                                       // 16 keys -> one chunk of hi and of lo codes
                 uint32_t hw[4], lw[4];
@@ -404,19 +406,25 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                     hw[w] = h01 | (h23 << 16);
                     lw[w] = l01 | (l23 << 16);
                 }
-                *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, half * 32 + c * 16)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                *reinterpret_cast<uint4 *>(smem + PF_OFF_P + sw128(row, 64 + half * 32 + c * 16)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) { hw8[c * 4 + w] = hw[w]; lw8[c * 4 + w] = lw[w]; }
+            }
+            tmem_st8_raw(p_tm + half * 8, hw8);
+            tmem_st8_raw(p_tm + 16 + half * 8, lw8);
             }
             l_run = fmaf(l_run, alpha, lsum);
             m_run = m_new;
             PF_TL(i, 6);
-            fence_async_smem();
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
             PF_TL(i, 7);
         }
         // ---- epilogue: O / l -> bf16 (with e4m3 both carry the factor 256); l = sum of the two halves' partial sums
+        // (a warp that skipped corrections may be two PVs behind the barrier's phase: one step at a time,
+        // so that a parity always names the phase it is meant for)
+        if (ok && n_tiles > 1) ok = mbar_wait(o_done, (n_tiles - 2) & 1);
         if (ok && n_tiles > 0) ok = mbar_wait(o_done, (n_tiles - 1) & 1);
         tc_fence_after();
         sm_mx[half * PF_BM + row] = l_run;
