@@ -1,8 +1,9 @@
 // Chunked prefill attention over the KV cache (e4m3 + scales, or bf16) on the 5th-generation
 // tensor cores (tcgen05.mma, accumulators and the A operands in tensor memory).
 //
-// One CTA per (128-query block, query head).  Keys stream in tiles of 64 through a TMA ring; per tile
-//     S[128 x 64]   = (Qhi + Qlo) K^T         tcgen05.mma kind::f8f6f4, K straight from the TMA tile
+// One CTA per (128-query block, query head).  Keys stream in tiles of 128 (e4m3) or 64 (bf16) through a
+// TMA ring; per tile
+//     S[128 x 128]  = (Qhi + Qlo) K^T         tcgen05.mma kind::f8f6f4, K straight from the TMA tile
 //     P             = exp2(S * k_scale * c + log2 v_scale - m)     256 threads, (query row, key half) each
 //     O[128 x 256] += (Phi + Plo) V           tcgen05.mma, V as an MN-major operand, same tile
 // The e4m3 codes of the cache feed the tensor cores unconverted.  The bf16 queries and the fp32
@@ -12,12 +13,14 @@
 // multiplies the fp32 score, the V scale is moved into the exponent of the probability.
 // Over a bf16 cache the same kernel issues kind::f16 MMAs on the bf16 rows as they are.
 //
-// Both A operands live in tensor memory: the query block is written there once (tcgen05.st by the
-// thread that owns the row), and the probabilities of a tile are written over the scores they
-// came from.  An MMA that takes A from shared memory re-reads the whole query block (64 KB) for
-// every key tile, which alone is more than the shared-memory bandwidth of the time the tile's
-// math takes; with A in tensor memory only the K and V tiles cross shared memory (64 KB per tile),
-// and the freed 80 KB hold more pipeline stages.
+// The probabilities of a tile are written over the scores they came from, in tensor memory, and
+// enter the PV product as a tensor-memory A operand (tcgen05.st by the thread that owns the row: no
+// shared-memory staging, no proxy fence).  A tcgen05.mma with N = 64 takes about 65 cycles where
+// its math needs 32 (measured: 16 of them per tile, 1040 cycles, with A in shared or in tensor
+// memory alike), so the e4m3 kernel works on 128 keys per tile: S is two buffers of 128 columns, O
+// 256 columns, which fills tensor memory, and the query block (hi + lo, 64 KB) stays in shared
+// memory.  A bf16 tile of 128 keys would be 128 KB of K and V per stage; the bf16 kernel keeps 64 keys
+// per tile and holds its query block in the 128 tensor-memory columns that leaves free.
 //
 // Warp roles: warps 0-7 softmax / correction / epilogue (two warpgroups; thread = one query row
 // = one TMEM lane, and one half of the tile's keys / of the output columns), warp 8 TMA
@@ -30,22 +33,19 @@
 namespace trb {
 
 constexpr int PF_BM = 128;              // queries per CTA
-constexpr int PF_BN = 64;               // keys per tile
 constexpr int PF_D = 256;               // head dim
-constexpr int PF_MAXST = 6;             // pipeline stages: 6 of (16 KB K, 16 KB V) for e4m3, 3 of (32 KB, 32 KB) for bf16
+constexpr int PF_MAXST = 3;             // pipeline stages of (32 KB K tile, 32 KB V tile): 2 for e4m3 (beside the query block), 3 for bf16
 constexpr int PF_SOFTMAX_THREADS = 256;     // two warpgroups: thread = (query row, half of the tile's keys)
 constexpr int PF_THREADS = PF_SOFTMAX_THREADS + 64;   // + TMA warp + MMA warp
-constexpr int PF_KV_BYTES = 192 * 1024;
-constexpr int PF_OFF_KV = 0;                           // stages of (K tile, V tile)
-constexpr int PF_OFF_SC = PF_OFF_KV + PF_KV_BYTES;     // [stages][2][64] floats
-constexpr int PF_OFF_FAC = PF_OFF_SC + PF_MAXST * 2 * PF_BN * 4;   // [3][3][64] floats: per-key factors of a tile, tiles i-1, i, i+1
-constexpr int PF_OFF_MX = PF_OFF_FAC + 3 * 3 * PF_BN * 4;          // [2][2][128] floats: row maxima of the two key halves
+constexpr int PF_TILE = 32 * 1024;      // 128 keys x 256 B (e4m3) or 64 keys x 512 B (bf16)
+constexpr int PF_Q_BYTES = PF_BM * PF_D;               // one e4m3 copy of the query block
+constexpr int PF_OFF_SC = 192 * 1024;                  // [3][2][keys per tile] floats (e4m3 only): the scales of tile i in slot i mod 3
+constexpr int PF_OFF_FAC = PF_OFF_SC + 3 * 2 * 128 * 4;            // [3][3][128] floats: per-key factors of a tile, tiles i-1, i, i+1
+constexpr int PF_OFF_MX = PF_OFF_FAC + 3 * 3 * 128 * 4;            // [2][2][128] floats: row maxima of the two key halves
 constexpr int PF_OFF_BAR = PF_OFF_MX + 2 * 2 * PF_BM * 4;
 constexpr int PF_SMEM = PF_OFF_BAR + 256 + 1024;
 constexpr int PF_TMEM_COLS = 512;
-constexpr int PF_TMEM_S = 0;            // S: two buffers, columns [0, 64) and [64, 128); P of a tile over the first 32 columns of its S
-constexpr int PF_TMEM_Q = 128;          // the query block: bf16 [128, 256), or e4m3 hi [128, 192) and lo [192, 256)
-constexpr int PF_TMEM_O = 256;          // O: columns [256, 512)
+constexpr int PF_TMEM_O = 256;          // O: columns [256, 512); S, P and (bf16) Q below it, see the kernel
 
 struct PrefillParams {
     const __nv_bfloat16 *q;
@@ -72,17 +72,23 @@ struct PrefillParams {
 template <bool FP8>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
-    constexpr int ROWB = PF_D * (FP8 ? 1 : 2), SEGS = ROWB / 128, TILE = PF_BN * ROWB, STAGES = FP8 ? PF_MAXST : PF_MAXST / 2;
-    constexpr int VB = FP8 ? 0 : PF_MAXST / 2;          // barrier index of a stage's V tile relative to its K tile
-    static_assert(STAGES * 2 * TILE == PF_KV_BYTES, "shared-memory layout");
+    constexpr int PF_BN = FP8 ? 128 : 64;               // keys per tile
+    constexpr int KPT = PF_BN / 2;                      // keys per softmax thread
+    constexpr int ROWB = PF_D * (FP8 ? 1 : 2), SEGS = ROWB / 128, TILE = PF_BN * ROWB, STAGES = FP8 ? 2 : 3;
+    constexpr int VB = PF_MAXST;                        // barrier index of a stage's V tile relative to its K tile
+    constexpr int PF_OFF_Q = 0, PF_OFF_KV = FP8 ? 2 * PF_Q_BYTES : 0;   // e4m3: Qhi, Qlo in shared memory, then the stages
+    // tensor memory below O: S in two buffers of PF_BN columns (P of a tile over the first columns of its S);
+    // bf16: the query block in columns [128, 256), two dims per column
+    constexpr int PF_TMEM_S = 0, PF_TMEM_Q = 128;
+    static_assert(TILE == PF_TILE && PF_OFF_KV + STAGES * 2 * TILE == PF_OFF_SC, "shared-memory layout");
     extern __shared__ uint8_t pf_smem_raw[];
     uint8_t *smem = pf_smem_raw + ((1024u - (smem_u32(pf_smem_raw) & 1023u)) & 1023u);
     float *sm_sc = reinterpret_cast<float *>(smem + PF_OFF_SC);
     float *sm_fac = reinterpret_cast<float *>(smem + PF_OFF_FAC);
     float *sm_mx = reinterpret_cast<float *>(smem + PF_OFF_MX);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + PF_OFF_BAR);
-    uint64_t *kv_full = bars, *kv_free = bars + PF_MAXST;
-    uint64_t *s_full = bars + 2 * PF_MAXST, *p_full = s_full + 2, *o_done = s_full + 3, *q_ready = s_full + 4;
+    uint64_t *kv_full = bars, *kv_free = bars + 2 * PF_MAXST;   // [s]: K tile (+ scales) of stage s, [VB + s]: its V tile
+    uint64_t *s_full = bars + 4 * PF_MAXST, *p_full = s_full + 2, *o_done = s_full + 3, *q_ready = s_full + 4;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_full + 5);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -97,9 +103,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #endif
 
     if (threadIdx.x == 0) {
-        // FP8: one barrier pair per stage (K + V tile + 64 scale pairs).  bf16: the stages' K tiles on
-        // barriers 0-2 and their V tiles on 3-5
-        for (int s = 0; s < PF_MAXST; ++s) { mbar_init(&kv_full[s], FP8 ? 33u : 1u); mbar_init(&kv_free[s], 1u); }
+        // K and V tiles have barriers of their own, so that a K tile is refilled as soon as its QK^T has run;
+        // the per-key scales of an e4m3 tile (cp.async by the 32 lanes of the producer) come with its K tile
+        for (int s = 0; s < PF_MAXST; ++s) {
+            mbar_init(&kv_full[s], FP8 ? 33u : 1u); mbar_init(&kv_full[VB + s], 1u);
+            mbar_init(&kv_free[s], 1u); mbar_init(&kv_free[VB + s], 1u);
+        }
         for (int b = 0; b < 2; ++b) mbar_init(&s_full[b], 1u);
         mbar_init(p_full, 8u); mbar_init(o_done, 1u); mbar_init(q_ready, 8u);
         mbar_fence_init();
@@ -117,48 +126,41 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             const int s = i % STAGES;
             const int row0 = i * PF_BN;
             uint8_t *kt = smem + PF_OFF_KV + s * 2 * TILE, *vt = kt + TILE;
-            if constexpr (!FP8) {
-                const uint32_t par = ((i / STAGES) & 1) ^ 1;
-                if (i >= STAGES && !mbar_wait(&kv_free[s], par)) break;            // QK^T of tile i-3 has run
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(&kv_full[s], TILE);
+            const uint32_t par = ((i / STAGES) & 1) ^ 1;
+            if (i >= STAGES && !mbar_wait(&kv_free[s], par)) break;                // QK^T of the stage's last tile has run
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&kv_full[s], TILE);
 #pragma unroll
-                    for (int sg = 0; sg < SEGS; ++sg) tma_load_4d(kt + sg * (PF_BN * 128), &tm_k, &kv_full[s], 0, sg, row0, j);
-                }
-                if (i >= STAGES && !mbar_wait(&kv_free[VB + s], par)) break;       // PV of tile i-3 has run
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(&kv_full[VB + s], TILE);
+                for (int sg = 0; sg < SEGS; ++sg) tma_load_4d(kt + sg * (PF_BN * 128), &tm_k, &kv_full[s], 0, sg, row0, j);
+            }
+            if constexpr (FP8) {
 #pragma unroll
-                    for (int sg = 0; sg < SEGS; ++sg) tma_load_4d(vt + sg * (PF_BN * 128), &tm_v, &kv_full[VB + s], 0, sg, row0, j);
-                }
-                __syncwarp();
-            } else {
-                if (i >= STAGES && !mbar_wait(&kv_free[s], ((i / STAGES) & 1) ^ 1)) break;
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(&kv_full[s], 2 * TILE);
-#pragma unroll
-                    for (int sg = 0; sg < SEGS; ++sg) {
-                        tma_load_4d(kt + sg * (PF_BN * 128), &tm_k, &kv_full[s], 0, sg, row0, j);
-                        tma_load_4d(vt + sg * (PF_BN * 128), &tm_v, &kv_full[s], 0, sg, row0, j);
-                    }
-                }
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
+                for (int hh = 0; hh < PF_BN / 32; ++hh) {
                     const long long r = (long long)row0 + lane + 32 * hh;
                     const bool ok = r < p.max_len;
                     const long long off = (long long)j * p.max_len + (ok ? r : 0);
-                    cp_async_4(&sm_sc[(s * 2 + 0) * PF_BN + lane + 32 * hh], p.ks + off, ok ? 4u : 0u);
-                    cp_async_4(&sm_sc[(s * 2 + 1) * PF_BN + lane + 32 * hh], p.vs + off, ok ? 4u : 0u);
+                    // slot i mod 3, not the stage: the slot is rewritten for tile i+3, whose K load waits for QK(i+1),
+                    // which is issued after the softmax pass that read this slot has published its P
+                    cp_async_4(&sm_sc[((i % 3) * 2 + 0) * PF_BN + lane + 32 * hh], p.ks + off, ok ? 4u : 0u);
+                    cp_async_4(&sm_sc[((i % 3) * 2 + 1) * PF_BN + lane + 32 * hh], p.vs + off, ok ? 4u : 0u);
                 }
                 cp_async_mbar_arrive_noinc(&kv_full[s]);
             }
+            if (i >= STAGES && !mbar_wait(&kv_free[VB + s], par)) break;           // PV of the stage's last tile has run
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&kv_full[VB + s], TILE);
+#pragma unroll
+                for (int sg = 0; sg < SEGS; ++sg) tma_load_4d(vt + sg * (PF_BN * 128), &tm_v, &kv_full[VB + s], 0, sg, row0, j);
+            }
+            __syncwarp();
         }
     } else if (warp == 9) {
         // ================================ MMA issuer ==================================
         // order on the tensor pipe: QK(0), QK(1), PV(0), QK(2), PV(1), ...  S is double-buffered so
         // that QK(i+1) runs while the softmax warps work on tile i.  The pipe runs in order of issue:
         // QK(i+2) overwrites the S buffer whose first columns hold P(i) only after PV(i) has read them.
-        const uint32_t q_hi = tmem + PF_TMEM_Q, q_lo = q_hi + 64;
+        const uint32_t q_tm = tmem + PF_TMEM_Q;                                             // bf16 query block
+        const uint32_t q_hi = smem_u32(smem + PF_OFF_Q), q_lo = q_hi + PF_Q_BYTES;          // e4m3 query block
         constexpr uint32_t IDESC_QK = FP8 ? umma_idesc_f8(PF_BM, PF_BN, false, false) : umma_idesc_bf16(PF_BM, PF_BN, false, false);
         constexpr uint32_t IDESC_PV = FP8 ? umma_idesc_f8(PF_BM, PF_D, false, true) : umma_idesc_bf16(PF_BM, PF_D, false, true);
         auto issue_qk = [&](int i) -> bool {
@@ -171,15 +173,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             tc_fence_after();
             if (lane == 0) {
                 if constexpr (FP8) {
-                    // S = Qhi K^T + Qlo K^T : 2 column blocks x 4 k-steps of 32 dims (8 TMEM columns of Q), hi then lo
+                    // S = Qhi K^T + Qlo K^T : 2 column blocks x 4 k-steps of 32 dims, hi then lo; N = 128 keys
 #pragma unroll
                     for (int term = 0; term < 2; ++term)
 #pragma unroll
                         for (int sg = 0; sg < 2; ++sg)
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
+                                const uint64_t a = umma_desc((term ? q_lo : q_hi) + sg * (PF_BM * 128) + k * 32, 16, 1024);
                                 const uint64_t bd = umma_desc(kt + sg * (PF_BN * 128) + k * 32, 16, 1024);
-                                tc_mma_f8_ts(tmem + PF_TMEM_S + b * PF_BN, (term ? q_lo : q_hi) + (sg * 4 + k) * 8, bd, IDESC_QK, (term | sg | k) ? 1u : 0u);
+                                tc_mma_f8(tmem + PF_TMEM_S + b * PF_BN, a, bd, IDESC_QK, (term | sg | k) ? 1u : 0u);
                             }
                 } else {
                     // S = Q K^T : 4 column blocks of 64 dims x 4 k-steps of 16 dims (8 TMEM columns of Q)
@@ -188,10 +191,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
                             const uint64_t bd = umma_desc(kt + sg * (PF_BN * 128) + k * 32, 16, 1024);
-                            tc_mma_bf16_ts(tmem + PF_TMEM_S + b * PF_BN, q_hi + (sg * 4 + k) * 8, bd, IDESC_QK, (sg | k) ? 1u : 0u);
+                            tc_mma_bf16_ts(tmem + PF_TMEM_S + b * PF_BN, q_tm + (sg * 4 + k) * 8, bd, IDESC_QK, (sg | k) ? 1u : 0u);
                         }
-                    tc_commit(&kv_free[s]);                                          // the K tile may be refilled
                 }
+                tc_commit(&kv_free[s]);                                              // the K tile may be refilled
                 tc_commit(&s_full[b]);
             }
             PF_TL(i, 11);
@@ -206,20 +209,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             const uint32_t p_tm = tmem + PF_TMEM_S + (i & 1) * PF_BN;                // P(i) lies over the first columns of S(i)
             if (i + 1 < n_tiles && !(ok = issue_qk(i + 1))) break;
             PF_TL(i, 12);
-            if constexpr (!FP8) { if (!(ok = mbar_wait(&kv_full[VB + s], (i / STAGES) & 1))) break; }   // V tile landed
+            if (!(ok = mbar_wait(&kv_full[VB + s], (i / STAGES) & 1))) break;      // V tile landed
             PF_TL(i, 13);
             if (!(ok = mbar_wait(p_full, i & 1))) break;                        // P of tile i staged (and O corrected)
             PF_TL(i, 14);
             tc_fence_after();
             if (lane == 0) {
                 if constexpr (FP8) {
-                    // O += Phi V + Plo V : P row = hi codes in columns [0, 16), lo in [16, 32); V tile MN-major, 32 keys per step
+                    // O += Phi V + Plo V : P row = hi codes in columns [0, 32), lo in [32, 64); V tile MN-major, 32 keys per step
 #pragma unroll
                     for (int term = 0; term < 2; ++term)
 #pragma unroll
-                        for (int k = 0; k < 2; ++k) {
+                        for (int k = 0; k < PF_BN / 32; ++k) {
                             const uint64_t bd = umma_desc(vt + k * (32 * 128), PF_BN * 128, 1024);
-                            tc_mma_f8_ts(tmem + PF_TMEM_O, p_tm + term * 16 + k * 8, bd, IDESC_PV, (i | term | k) ? 1u : 0u);
+                            tc_mma_f8_ts(tmem + PF_TMEM_O, p_tm + term * (PF_BN / 4) + k * 8, bd, IDESC_PV, (i | term | k) ? 1u : 0u);
                         }
                 } else {
                     // O += P V : P row = 64 keys in 32 columns; V tile MN-major (four 64-dim column blocks), 16 keys per step
@@ -238,7 +241,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     } else {
         // ============ softmax / correction / epilogue: warps 0-7, thread = (row, key half) ============
         const int row = (warp & 3) * 32 + lane;                               // query row = TMEM lane
-        const int half = warp >> 2;                                           // keys [32 half, 32 half + 32) of a tile
+        const int half = warp >> 2;                                           // keys [KPT half, KPT half + KPT) of a tile
         const bool row_ok = row < rows_here;
         const long long qpos = p.pos + q0 + row;
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -275,18 +278,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             if (e > 90) e = 90;
             const float sc = row_ok ? __uint_as_float((uint32_t)(127 + 7 - e) << 23) : 0.f;
             qinv = __uint_as_float((uint32_t)(127 - 7 + e) << 23);
-            uint32_t hw[32], lw[32];                                           // this thread's 128 dims: 32 columns of hi and of lo codes
+            for (int cc = 0; cc < PF_D / 32; ++cc) {                           // this thread's 8 chunks of 16 dims
+                const int c = half * (PF_D / 32) + cc;
+                uint32_t hw[4], lw[4];
 #pragma unroll
-            for (int w = 0; w < 32; ++w) {
-                const uint2 raw = *reinterpret_cast<const uint2 *>(qp + half * (PF_D / 2) + w * 4);
-                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
-                const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
-                const float y[4] = {a.x * sc, a.y * sc, b.x * sc, b.y * sc};
-                pf_split4(y, hw[w], lw[w]);
+                for (int w = 0; w < 4; ++w) {
+                    const uint2 raw = *reinterpret_cast<const uint2 *>(qp + c * 16 + w * 4);
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+                    const float y[4] = {a.x * sc, a.y * sc, b.x * sc, b.y * sc};
+                    pf_split4(y, hw[w], lw[w]);
+                }
+                const uint32_t off = (c >> 3) * (PF_BM * 128) + sw128(row, (c & 7) * 16);
+                *reinterpret_cast<uint4 *>(smem + PF_OFF_Q + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                *reinterpret_cast<uint4 *>(smem + PF_OFF_Q + PF_Q_BYTES + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
             }
-            tmem_st32_raw(lane_addr + PF_TMEM_Q + half * 32, hw);
-            tmem_st32_raw(lane_addr + PF_TMEM_Q + 64 + half * 32, lw);
-            tmem_st_wait();
+            fence_async_smem();
         }
         tc_fence_before();
         __syncwarp();
@@ -317,7 +324,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                 if (!(ok = mbar_wait(&kv_full[s1], ((i + 1) / STAGES) & 1))) break;
                 if (tid < PF_BN) {
                     float *fn = sm_fac + ((i + 1) % 3) * 3 * PF_BN;
-                    const float kscv = sm_sc[(s1 * 2 + 0) * PF_BN + tid], vscv = sm_sc[(s1 * 2 + 1) * PF_BN + tid];
+                    const float kscv = sm_sc[(((i + 1) % 3) * 2 + 0) * PF_BN + tid], vscv = sm_sc[(((i + 1) % 3) * 2 + 1) * PF_BN + tid];
                     fn[tid] = kscv * p.scale_log2;
                     fn[PF_BN + tid] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
                     fn[2 * PF_BN + tid] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
@@ -327,18 +334,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             if (!(ok = mbar_wait(&s_full[b], (i >> 1) & 1))) break;
             PF_TL(i, 1);
             tc_fence_after();
-            float sv[32];
-            tmem_ld32(lane_addr + PF_TMEM_S + b * PF_BN + half * 32, sv);
+            float sv[KPT];
+#pragma unroll
+            for (int c = 0; c < KPT / 32; ++c)
+                tmem_ld32(lane_addr + PF_TMEM_S + b * PF_BN + half * KPT + c * 32, *reinterpret_cast<float (*)[32]>(&sv[c * 32]));
             PF_TL(i, 2);
             // scores -> exponent domain (t = raw * k_scale * c * q_inv + log2 v_scale), row maximum
-            const long long key0 = (long long)i * PF_BN + half * 32;
-            const float *fa_ = fac + half * 32, *fb_ = fac + PF_BN + half * 32, *fr_ = fac + 2 * PF_BN + half * 32;
+            const long long key0 = (long long)i * PF_BN + half * KPT;
+            const float *fa_ = fac + half * KPT, *fb_ = fac + PF_BN + half * KPT, *fr_ = fac + 2 * PF_BN + half * KPT;
             if constexpr (!FP8) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) sv[c] *= p.scale_log2;
+                for (int c = 0; c < KPT; ++c) sv[c] *= p.scale_log2;
             } else
 #pragma unroll
-            for (int c4 = 0; c4 < 8; ++c4) {
+            for (int c4 = 0; c4 < KPT / 4; ++c4) {
                 const float4 fa = *reinterpret_cast<const float4 *>(fa_ + c4 * 4);
                 const float4 fb = *reinterpret_cast<const float4 *>(fb_ + c4 * 4);
                 sv[c4 * 4 + 0] = fmaf(sv[c4 * 4 + 0] * fa.x, qinv, fb.x);
@@ -346,14 +355,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                 sv[c4 * 4 + 2] = fmaf(sv[c4 * 4 + 2] * fa.z, qinv, fb.z);
                 sv[c4 * 4 + 3] = fmaf(sv[c4 * 4 + 3] * fa.w, qinv, fb.w);
             }
-            if (key0 + 31 > qpos_warp_min || warp_has_padding) {               // the tile crosses this warp's diagonal
+            if (key0 + KPT - 1 > qpos_warp_min || warp_has_padding) {          // the tile crosses this warp's diagonal
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
+                for (int c = 0; c < KPT; ++c)
                     if (!(key0 + c <= qpos && row_ok)) sv[c] = -INFINITY;
             }
-            float mt = -INFINITY;
+            float mt4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 32; ++c) mt = fmaxf(mt, sv[c]);
+            for (int c = 0; c < KPT; ++c) mt4[c & 3] = fmaxf(mt4[c & 3], sv[c]);
+            float mt = fmaxf(fmaxf(mt4[0], mt4[1]), fmaxf(mt4[2], mt4[3]));
             mxbuf[half * PF_BM + row] = mt;
             PF_TL(i, 3);
             named_barrier(1, PF_SOFTMAX_THREADS);
@@ -390,27 +400,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                 }
                 tmem_st16_raw(p_tm + half * 16, w);
             } else {
-            uint32_t hw8[8], lw8[8];                                            // this thread's 32 keys: 8 columns of hi and of lo codes
+                // hi codes of the tile's keys in columns [0, PF_BN / 4), lo codes in the next PF_BN / 4; four keys per column
+                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {                                       // 16 keys -> one chunk of hi and of lo codes
-                uint32_t hw[4], lw[4];
+                for (int g32 = 0; g32 < KPT / 32; ++g32) {                      // 32 keys -> 8 columns of hi and of lo codes
+                    uint32_t hw8[8], lw8[8];
 #pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const float4 fr = *reinterpret_cast<const float4 *>(fr_ + c * 16 + w * 4);
-                    const float p0 = fast_exp2(sv[c * 16 + w * 4 + 0] - m_off), p1 = fast_exp2(sv[c * 16 + w * 4 + 1] - m_off);
-                    const float p2 = fast_exp2(sv[c * 16 + w * 4 + 2] - m_off), p3 = fast_exp2(sv[c * 16 + w * 4 + 3] - m_off);
-                    lsum = fmaf(p0, fr.x, lsum); lsum = fmaf(p1, fr.y, lsum); lsum = fmaf(p2, fr.z, lsum); lsum = fmaf(p3, fr.w, lsum);
-                    uint32_t h01, l01, h23, l23;
-                    pf_split2_h(p0, p1, h01, l01);
-                    pf_split2_h(p2, p3, h23, l23);
-                    hw[w] = h01 | (h23 << 16);
-                    lw[w] = l01 | (l23 << 16);
+                    for (int w = 0; w < 8; ++w) {
+                        const int k0 = g32 * 32 + w * 4;
+                        const float4 fr = *reinterpret_cast<const float4 *>(fr_ + k0);
+                        const float p0 = fast_exp2(sv[k0 + 0] - m_off), p1 = fast_exp2(sv[k0 + 1] - m_off);
+                        const float p2 = fast_exp2(sv[k0 + 2] - m_off), p3 = fast_exp2(sv[k0 + 3] - m_off);
+                        ls4[0] = fmaf(p0, fr.x, ls4[0]); ls4[1] = fmaf(p1, fr.y, ls4[1]); ls4[2] = fmaf(p2, fr.z, ls4[2]); ls4[3] = fmaf(p3, fr.w, ls4[3]);
+                        uint32_t h01, l01, h23, l23;
+                        pf_split2_h(p0, p1, h01, l01);
+                        pf_split2_h(p2, p3, h23, l23);
+                        hw8[w] = h01 | (h23 << 16);
+                        lw8[w] = l01 | (l23 << 16);
+                    }
+                    tmem_st8_raw(p_tm + half * (KPT / 4) + g32 * 8, hw8);
+                    tmem_st8_raw(p_tm + PF_BN / 4 + half * (KPT / 4) + g32 * 8, lw8);
                 }
-#pragma unroll
-                for (int w = 0; w < 4; ++w) { hw8[c * 4 + w] = hw[w]; lw8[c * 4 + w] = lw[w]; }
-            }
-            tmem_st8_raw(p_tm + half * 8, hw8);
-            tmem_st8_raw(p_tm + 16 + half * 8, lw8);
+                lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
             }
             l_run = fmaf(l_run, alpha, lsum);
             m_run = m_new;
@@ -469,15 +480,16 @@ extern "C" int trb_attn_prefill(const trb_cache_t *cache, const void *q, void *o
     if (c.d != PF_D || c.ring > 0 || c.sharded) return TRB_E_UNSUPPORTED;
     if (pos + t > c.max_len) return TRB_E_CAPACITY;
     if (((uintptr_t)q | (uintptr_t)out) & 15) return TRB_E_ALIGN;
-    if (c.max_len >= (1LL << 31) - 64) return TRB_E_UNSUPPORTED;
+    if (c.max_len >= (1LL << 31) - 128) return TRB_E_UNSUPPORTED;
     PrefillParams p;
     p.q = (const __nv_bfloat16 *)q; p.out = (__nv_bfloat16 *)out; p.ks = c.k_scale; p.vs = c.v_scale;
     p.t = t; p.hq = hq; p.hkv = c.hkv; p.g = hq / c.hkv; p.pos = pos; p.max_len = c.max_len;
     p.scale_log2 = scale * 1.4426950408889634f;
     CUtensorMap mk, mv;
     const int row_bytes = PF_D * (c.fp8 ? 1 : 2);
-    if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, row_bytes, PF_BN, &mk))) return rc;
-    if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, row_bytes, PF_BN, &mv))) return rc;
+    const int tile_rows = c.fp8 ? 128 : 64;
+    if ((rc = get_row_tile_map(c.k, c.max_len, c.hkv, row_bytes, tile_rows, &mk))) return rc;
+    if ((rc = get_row_tile_map(c.v, c.max_len, c.hkv, row_bytes, tile_rows, &mv))) return rc;
     static bool attr_set[64] = {};
     int dev = 0;
     TRB_CUDA_CHECK(cudaGetDevice(&dev));
