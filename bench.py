@@ -85,15 +85,33 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML queries from a thread
+    every 20 ms (read-only), or `nvidia-smi -lms 100` where the NVML binding is missing."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.samples, self.proc = index, [], None
+        self.index, self.samples, self.proc, self.nvml, self.stop = index, [], None, None, threading.Event()
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
 
     def __enter__(self):
+        try:
+            self.nvml = self._nvml_handle()
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -104,11 +122,28 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def _poll(self):
+        nv, h = self.nvml
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        while True:
+            try:
+                mhz, mx = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+                r = int(get_reasons(h))
+                self.samples.append(",".join([str(mhz), str(mx)] + ["Active" if r & bits[n] else "Not Active" for n in self.NAMES]))
+            except Exception:
+                pass
+            if self.stop.wait(0.02):
+                return
+
     def _read(self):
         for line in self.proc.stdout:
             self.samples.append(line.strip())
 
     def __exit__(self, *exc):
+        self.stop.set()
+        if self.nvml is not None:
+            self.thread.join(timeout=1)
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -118,7 +153,6 @@ class ClockSampler:
 
     def summary(self):
         mhz, mx, reasons = [], 0, set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for s in self.samples:
             parts = [x.strip() for x in s.split(",")]
             if len(parts) < 6:
@@ -127,7 +161,7 @@ class ClockSampler:
                 mhz.append(float(parts[0])); mx = max(mx, float(parts[1]))
             except ValueError:
                 continue
-            for n, v in zip(names, parts[2:6]):
+            for n, v in zip(self.NAMES, parts[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx or None,

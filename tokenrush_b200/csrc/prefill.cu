@@ -61,10 +61,16 @@ struct PrefillParams {
 // are written as bf16; no scales, no hi + lo terms.  Rows are 512 bytes (four 128-byte column
 // blocks), tiles 32 KB, three stages; K and V tiles have barriers of their own, so that a K tile is
 // refilled as soon as its QK^T has run.
-// Diagnostic build only: the last query block of head 0 stamps clock64 at fixed points of tiles 64..95
+__device__ __forceinline__ float pf_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// Diagnostic build only: the last query block of head 0 stamps clock64 at fixed points of 32 late tiles
 // (slots 0-7: lane 0 of softmax warp 0, slots 8-15: lane 0 of the MMA warp) into timeline launch slot 63.
 #ifdef TRB_TIMELINE
-#define PF_TL(i, slot) do { if (lane == 0 && tl_on && (i) >= 64 && (i) < 96) g_timeline[63][(i) - 64][slot] = (unsigned long long)clock64(); } while (0)
+#define PF_TL(i, slot) do { if (lane == 0 && tl_on && (i) >= tl_base && (i) < tl_base + 32) g_timeline[63][(i) - tl_base][slot] = (unsigned long long)clock64(); } while (0)
 #else
 #define PF_TL(i, slot) do { } while (0)
 #endif
@@ -100,6 +106,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     const int n_tiles = (int)((hi + PF_BN - 1) / PF_BN);
 #ifdef TRB_TIMELINE
     const bool tl_on = blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && (warp == 0 || warp == 9);
+    const int tl_base = n_tiles > 48 ? n_tiles - 48 : 0;      // late tiles: row maxima rarely move there
 #endif
 
     if (threadIdx.x == 0) {
@@ -343,17 +350,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             const long long key0 = (long long)i * PF_BN + half * KPT;
             const float *fa_ = fac + half * KPT, *fb_ = fac + PF_BN + half * KPT, *fr_ = fac + 2 * PF_BN + half * KPT;
             if constexpr (!FP8) {
+                const float2 sl2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
-                for (int c = 0; c < KPT; ++c) sv[c] *= p.scale_log2;
-            } else
+                for (int c = 0; c < KPT / 2; ++c) {
+                    const float2 a = __fmul2_rn(make_float2(sv[2 * c], sv[2 * c + 1]), sl2);
+                    sv[2 * c] = a.x; sv[2 * c + 1] = a.y;
+                }
+            } else {
+                const float2 qinv2 = make_float2(qinv, qinv);
 #pragma unroll
-            for (int c4 = 0; c4 < KPT / 4; ++c4) {
-                const float4 fa = *reinterpret_cast<const float4 *>(fa_ + c4 * 4);
-                const float4 fb = *reinterpret_cast<const float4 *>(fb_ + c4 * 4);
-                sv[c4 * 4 + 0] = fmaf(sv[c4 * 4 + 0] * fa.x, qinv, fb.x);
-                sv[c4 * 4 + 1] = fmaf(sv[c4 * 4 + 1] * fa.y, qinv, fb.y);
-                sv[c4 * 4 + 2] = fmaf(sv[c4 * 4 + 2] * fa.z, qinv, fb.z);
-                sv[c4 * 4 + 3] = fmaf(sv[c4 * 4 + 3] * fa.w, qinv, fb.w);
+                for (int c4 = 0; c4 < KPT / 4; ++c4) {                             // two scores per FMA-pipe instruction
+                    const float4 fa = *reinterpret_cast<const float4 *>(fa_ + c4 * 4);
+                    const float4 fb = *reinterpret_cast<const float4 *>(fb_ + c4 * 4);
+                    const float2 a = __ffma2_rn(__fmul2_rn(make_float2(sv[c4 * 4 + 0], sv[c4 * 4 + 1]), make_float2(fa.x, fa.y)), qinv2, make_float2(fb.x, fb.y));
+                    const float2 c = __ffma2_rn(__fmul2_rn(make_float2(sv[c4 * 4 + 2], sv[c4 * 4 + 3]), make_float2(fa.z, fa.w)), qinv2, make_float2(fb.z, fb.w));
+                    sv[c4 * 4 + 0] = a.x; sv[c4 * 4 + 1] = a.y; sv[c4 * 4 + 2] = c.x; sv[c4 * 4 + 3] = c.y;
+                }
             }
             if (key0 + KPT - 1 > qpos_warp_min || warp_has_padding) {          // the tile crosses this warp's diagonal
 #pragma unroll
@@ -362,7 +374,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             }
             float mt4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < KPT; ++c) mt4[c & 3] = fmaxf(mt4[c & 3], sv[c]);
+            for (int c = 0; c < KPT / 2; ++c) mt4[c & 3] = pf_max3(mt4[c & 3], sv[2 * c], sv[2 * c + 1]);
             float mt = fmaxf(fmaxf(mt4[0], mt4[1]), fmaxf(mt4[2], mt4[3]));
             mxbuf[half * PF_BM + row] = mt;
             PF_TL(i, 3);
@@ -401,7 +413,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                 tmem_st16_raw(p_tm + half * 16, w);
             } else {
                 // hi codes of the tile's keys in columns [0, PF_BN / 4), lo codes in the next PF_BN / 4; four keys per column
-                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+                const float2 nm2 = make_float2(-m_off, -m_off);
+                float2 lsa = make_float2(0.f, 0.f), lsb = make_float2(0.f, 0.f);
 #pragma unroll
                 for (int g32 = 0; g32 < KPT / 32; ++g32) {                      // 32 keys -> 8 columns of hi and of lo codes
                     uint32_t hw8[8], lw8[8];
@@ -409,19 +422,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                     for (int w = 0; w < 8; ++w) {
                         const int k0 = g32 * 32 + w * 4;
                         const float4 fr = *reinterpret_cast<const float4 *>(fr_ + k0);
-                        const float p0 = fast_exp2(sv[k0 + 0] - m_off), p1 = fast_exp2(sv[k0 + 1] - m_off);
-                        const float p2 = fast_exp2(sv[k0 + 2] - m_off), p3 = fast_exp2(sv[k0 + 3] - m_off);
-                        ls4[0] = fmaf(p0, fr.x, ls4[0]); ls4[1] = fmaf(p1, fr.y, ls4[1]); ls4[2] = fmaf(p2, fr.z, ls4[2]); ls4[3] = fmaf(p3, fr.w, ls4[3]);
+                        const float2 d01 = __fadd2_rn(make_float2(sv[k0 + 0], sv[k0 + 1]), nm2);
+                        const float2 d23 = __fadd2_rn(make_float2(sv[k0 + 2], sv[k0 + 3]), nm2);
+                        const float2 p01 = make_float2(fast_exp2(d01.x), fast_exp2(d01.y));
+                        const float2 p23 = make_float2(fast_exp2(d23.x), fast_exp2(d23.y));
+                        lsa = __ffma2_rn(p01, make_float2(fr.x, fr.y), lsa);
+                        lsb = __ffma2_rn(p23, make_float2(fr.z, fr.w), lsb);
                         uint32_t h01, l01, h23, l23;
-                        pf_split2_h(p0, p1, h01, l01);
-                        pf_split2_h(p2, p3, h23, l23);
+                        pf_split2_h(p01.x, p01.y, h01, l01);
+                        pf_split2_h(p23.x, p23.y, h23, l23);
                         hw8[w] = h01 | (h23 << 16);
                         lw8[w] = l01 | (l23 << 16);
                     }
                     tmem_st8_raw(p_tm + half * (KPT / 4) + g32 * 8, hw8);
                     tmem_st8_raw(p_tm + PF_BN / 4 + half * (KPT / 4) + g32 * 8, lw8);
                 }
-                lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+                lsum = (lsa.x + lsa.y) + (lsb.x + lsb.y);
             }
             l_run = fmaf(l_run, alpha, lsum);
             m_run = m_new;
