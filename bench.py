@@ -354,6 +354,7 @@ def run_decode(name: str, args, steps: int, warmup: int, blocks: int, cpu_second
     def step_body(count=False):
         nonlocal launches_per_step
         n = 0
+        lib_before = tb._lib.lib().trb_launch_count()
         for l in range(LAYERS):
             if world > 1:
                 shard.sharded_decode_layer(state, l, d_q[l], d_k[l], d_v[l], cfg, xchg, out=d_out[l])
@@ -373,7 +374,9 @@ def run_decode(name: str, args, steps: int, warmup: int, blocks: int, cpu_second
             tb.fused.cursor_advance(state.pos_t, m)
         n += 1
         if count:
-            launches_per_step = n
+            # the library's own count of what this step launched (a decode call may be two kernels: the scan
+            # and the merge of its rows); n, the number of calls, is the floor
+            launches_per_step = max(n, int(tb._lib.lib().trb_launch_count() - lib_before))
 
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())

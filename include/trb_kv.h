@@ -97,6 +97,10 @@ const char *trb_strerror(int code);
  * Results are the same in all modes.  Returns TRB_E_ARG for another value. */
 int trb_set_programmatic_launch(int mode);
 
+/* Kernels launched by this library in this process so far (every entry point counts its own launches,
+ * also while a stream is being captured: a captured launch counts once, not once per replay). */
+unsigned long long trb_launch_count(void);
+
 /* Poll limits of the bounded device-side waits on the current device (0 restores a default):
  * pipeline_polls - shared-memory pipeline barriers (default 2^20, about a second);
  * tail_polls     - split partials in the decode tail (default 2^17);

@@ -58,6 +58,7 @@ SIGNATURES = {
     "trb_strerror": (C.c_char_p, [C.c_int]),
     "trb_set_programmatic_launch": (C.c_int, [C.c_int]),
     "trb_set_wait_limits": (C.c_int, [C.c_uint32, C.c_uint32, C.c_uint32]),
+    "trb_launch_count": (C.c_ulonglong, []),
     "trb_set_decode_tensor_rows": (C.c_int, [C.c_int32]),
     "trb_device_status": (C.c_int, [C.POINTER(C.c_uint32)]),
     "trb_kv_append": (C.c_int, [C.POINTER(Cache), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32,

@@ -249,6 +249,7 @@ void pdl_note_fence(cudaStream_t st);
 
 // Host: launch with (or without) the programmatic-stream-serialization attribute.
 inline bool pdl_enabled() { return pdl_mode() != 0; }
+void note_launch();                               // counts the kernels this library launches (trb_launch_count)
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args &&...args) {
     cudaLaunchConfig_t cfg = {};
@@ -258,6 +259,7 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
+    note_launch();
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
 }
 

@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -144,13 +145,21 @@ int pdl_plan_decode(cudaStream_t st, const void *cache_k, const trb_cursor_t *po
     return flags;
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// A kernel launched without the programmatic attribute: everything before it on the stream is
+// complete when it runs (every such launch site calls this right before its one launch).
 void pdl_note_fence(cudaStream_t st) {
+    note_launch();
     std::lock_guard<std::mutex> lock(g_track_mu);
     auto it = g_track.find(st);
     if (it != g_track.end()) it->second.s.clear();
 }
 
 }  // namespace trb
+
+extern "C" unsigned long long trb_launch_count(void) { return trb::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" int trb_set_programmatic_launch(int mode) {
     if (mode < 0 || mode > 2) return TRB_E_ARG;
