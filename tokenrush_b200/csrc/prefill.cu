@@ -95,7 +95,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + PF_OFF_BAR);
     uint64_t *kv_full = bars, *kv_free = bars + 2 * PF_MAXST;   // [s]: K tile (+ scales) of stage s, [VB + s]: its V tile
     uint64_t *s_full = bars + 4 * PF_MAXST, *p_full = s_full + 2, *o_done = s_full + 3, *q_ready = s_full + 4;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_full + 5);
+    uint64_t *fac_full = s_full + 5;                            // [3]: the factor table of tile i (slot i mod 3) is written
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(s_full + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int qb = blockIdx.x, h = blockIdx.y, j = h / p.g;
@@ -117,6 +118,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             mbar_init(&kv_free[s], 1u); mbar_init(&kv_free[VB + s], 1u);
         }
         for (int b = 0; b < 2; ++b) mbar_init(&s_full[b], 1u);
+        for (int b = 0; b < 3; ++b) mbar_init(&fac_full[b], 1u);
         mbar_init(p_full, 8u); mbar_init(o_done, 1u); mbar_init(q_ready, 8u);
         mbar_fence_init();
         tma_prefetch_desc(&tm_k); tma_prefetch_desc(&tm_v);
@@ -129,6 +131,24 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
 
     if (warp == 8) {
         // ================================ TMA producer ================================
+        // Between its loads this warp also turns the scales of a landed e4m3 tile into the per-key factors the
+        // softmax threads use (score scale, log2 of the V scale, 1 / V scale), four keys per lane, a tile ahead
+        // of the softmax pass that reads them.
+        auto build_factors = [&](int t) -> bool {
+            if (!mbar_wait(&kv_full[t % STAGES], (t / STAGES) & 1)) return false;   // the tile's scales have landed
+            float *fn = sm_fac + (t % 3) * 3 * PF_BN;
+#pragma unroll
+            for (int hh = 0; hh < PF_BN / 32; ++hh) {
+                const int k = lane + 32 * hh;
+                const float kscv = sm_sc[((t % 3) * 2 + 0) * PF_BN + k], vscv = sm_sc[((t % 3) * 2 + 1) * PF_BN + k];
+                fn[k] = kscv * p.scale_log2;
+                fn[PF_BN + k] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
+                fn[2 * PF_BN + k] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&fac_full[t % 3]);
+            return true;
+        };
         for (int i = 0; i < n_tiles; ++i) {
             const int s = i % STAGES;
             const int row0 = i * PF_BN;
@@ -153,6 +173,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
                 }
                 cp_async_mbar_arrive_noinc(&kv_full[s]);
             }
+            // (before the wait for the V buffer, which ends a softmax pass later than the wait above: the table of
+            // tile i-1 is then ready a whole pass before it is read)
+            if constexpr (FP8) { if (i >= 1 && !build_factors(i - 1)) break; }
             if (i >= STAGES && !mbar_wait(&kv_free[VB + s], par)) break;           // PV of the stage's last tile has run
             if (lane == 0) {
                 mbar_arrive_expect_tx(&kv_full[VB + s], TILE);
@@ -161,6 +184,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
             }
             __syncwarp();
         }
+        if constexpr (FP8) { if (n_tiles > 0) build_factors(n_tiles - 1); }
     } else if (warp == 9) {
         // ================================ MMA issuer ==================================
         // order on the tensor pipe: QK(0), QK(1), PV(0), QK(2), PV(1), ...  S is double-buffered so
@@ -310,35 +334,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__
         bool ok = true;
         const long long qpos_warp_min = p.pos + q0 + (warp & 3) * 32;            // lane 0's position
         const bool warp_has_padding = (warp & 3) * 32 + 31 >= rows_here;
-        if (FP8 && n_tiles > 0) {
-            ok = mbar_wait(&kv_full[0], 0);
-            if (ok && tid < PF_BN) {
-                const float kscv = sm_sc[tid], vscv = sm_sc[PF_BN + tid];
-                sm_fac[tid] = kscv * p.scale_log2;
-                sm_fac[PF_BN + tid] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
-                sm_fac[2 * PF_BN + tid] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
-            }
-            named_barrier(1, PF_SOFTMAX_THREADS);
-        }
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int b = i & 1;
-            // per-key factors (score scale, log2 of the V scale, 1 / V scale), once per CTA and one tile
-            // ahead: the table of tile i+1 is written here and published by this tile's barrier below
-            float *fac = sm_fac + (i % 3) * 3 * PF_BN;
+            float *fac = sm_fac + (i % 3) * 3 * PF_BN;            // per-key factors of this tile, written by the producer warp
             float *mxbuf = sm_mx + b * 2 * PF_BM;
-            if (FP8 && i + 1 < n_tiles) {
-                const int s1 = (i + 1) % STAGES;
-                if (!(ok = mbar_wait(&kv_full[s1], ((i + 1) / STAGES) & 1))) break;
-                if (tid < PF_BN) {
-                    float *fn = sm_fac + ((i + 1) % 3) * 3 * PF_BN;
-                    const float kscv = sm_sc[(((i + 1) % 3) * 2 + 0) * PF_BN + tid], vscv = sm_sc[(((i + 1) % 3) * 2 + 1) * PF_BN + tid];
-                    fn[tid] = kscv * p.scale_log2;
-                    fn[PF_BN + tid] = vscv > 0.f ? __log2f(vscv) : -INFINITY;
-                    fn[2 * PF_BN + tid] = vscv > 0.f ? __fdividef(1.f, vscv) : 0.f;
-                }
-            }
             PF_TL(i, 0);
             if (!(ok = mbar_wait(&s_full[b], (i >> 1) & 1))) break;
+            if constexpr (FP8) { if (!(ok = mbar_wait(&fac_full[i % 3], (i / 3) & 1))) break; }
             PF_TL(i, 1);
             tc_fence_after();
             float sv[KPT];
