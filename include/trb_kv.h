@@ -269,8 +269,9 @@ int trb_add_rmsnorm(const void *x, const void *h, int32_t h_splits, const void *
 
 /* ------------------------------------------------------------------ chunked prefill
  * Replaces fused.attn_prefill_fused (tokenrush/fused.py:476-533): t queries q [t, hq, d] bf16 at
- * host position pos over cache rows 0..pos+t-1 (the chunk's own rows already appended in
- * FP8 form), query i sees keys <= pos+i; out [t, hq, d] bf16, ungated. */
+ * host position pos over cache rows 0..pos+t-1 (the chunk's own rows already appended, e4m3 +
+ * scales or bf16 as the cache is), query i sees keys <= pos+i; out [t, hq, d] bf16, ungated.
+ * Head dim 256, no ring, no shard (TRB_E_UNSUPPORTED otherwise). */
 int trb_attn_prefill(const trb_cache_t *cache, const void *q, void *out, int32_t t, int32_t hq,
                      int64_t pos, float scale, trb_stream_t stream);
 
