@@ -97,3 +97,26 @@ def test_prefill_8192_over_131072(tb):
     want = O.attn_rows_over_cache(ref, 0, qb[rows], pos, row_pos=pos + np.asarray(rows))   # each row has its own causal limit
     assert_attn_close(got[rows], want, "prefill 8192 over 131072")
     assert tb._lib.device_status() == 0
+
+
+def test_prefill_2048_over_65536_bf16_cache(tb):
+    """The bf16-cache instance of the prefill kernel (kind::f16 MMAs, 64-key tiles, query block in tensor
+    memory) at a long context: 1056 key tiles per query block, 16 query blocks; the chunk's rows are stored
+    as they are, sampled query rows x all heads against fp32 oracle attention over the device's rows."""
+    pos, T = 65536, 2048
+    cfg = tb.AttnConfig(n_attn=1)
+    st = tb.State(cfg, pos + T + 64, "cuda", kv_dtype=torch.bfloat16)
+    fill_cache_gpu(tb, st, 0, pos, seed=4)
+    kb, vb = O.seeded_bf16(61, HKV, T, D), O.seeded_bf16(62, HKV, T, D)
+    qb = O.seeded_bf16(63, T, HQ, D)
+    tb.fused.kv_write_prefill(to_dev(kb), to_dev(vb), st, 0, pos)
+    o = tb.fused.attn_prefill_fused(to_dev(qb), st.k[0], st.v[0], pos, cfg)
+    torch.cuda.synchronize()
+    from _util import bits_of
+    assert np.array_equal(bits_of(st.k[0][:, pos:pos + T]), kb) and np.array_equal(bits_of(st.v[0][:, pos:pos + T]), vb)
+    rows = sorted(set([0, 1, 63, 64, 127, 128, 129, 1023, 1024, T - 129, T - 128, T - 2, T - 1] +
+                      list(np.linspace(5, T - 7, 19).astype(int))))[:32]
+    ref = oracle_state_from(st)
+    want = O.attn_rows_over_cache(ref, 0, qb[rows], pos, row_pos=pos + np.asarray(rows))
+    assert_attn_close(f32_of(o)[rows], want, "bf16 prefill 2048 over 65536")
+    assert tb._lib.device_status() == 0

@@ -57,15 +57,17 @@ def attn_decode_bucket(q, K, V, pos_t):
 
 def attn_prefill(q, K, V, pos: int, block: int = 1024):
     """q [Hq, T, D] for positions pos..pos+T-1; K, V [Hkv, pos+T, D].  Causal over the whole cache:
-    query i sees keys <= pos+i.  Rows go through the M-row decode kernel in groups (the tensor-core
-    prefill kernel reads the fp8 cache only)."""
+    query i sees keys <= pos+i.  256-dim heads take the tensor-core prefill kernel (bf16 MMAs over the
+    rows as they are); other head sizes go through the M-row decode kernel in groups of rows."""
     hq, t, d = q.shape
     hkv = K.shape[0]
     assert K.shape[1] == pos + t
     kc, vc = _as_cache(K, V)
+    qt = q.transpose(0, 1).contiguous()                      # [T, Hq, D]
+    if d == 256:
+        return fused.attn_prefill_fused(qt, kc, vc, pos, _Geom(hq, hkv, d)).transpose(0, 1)
     m_max = max(1, 48 // (hq // hkv))
     out = torch.empty_like(q)
-    qt = q.transpose(0, 1).contiguous()                      # [T, Hq, D]
     for s0 in range(0, t, m_max):
         m = min(m_max, t - s0)
         o = fused._decode(qt[s0:s0 + m].reshape(m, hq * d), kc, vc, pos + s0, hq, hkv, d, None, None, new_rows=1)
