@@ -107,3 +107,22 @@ def test_prefill_over_a_bf16_cache(tb, hq, hkv, d, pos, T):
     want = O.attn_prefill(O.bf16_bits_to_f32(qb), O.bf16_bits_to_f32(kb), O.bf16_bits_to_f32(vb), pos)
     assert_attn_close_bf16_p(f32_of(o), want, "prefill over a bf16 cache")
     assert tb._lib.device_status() == 0
+
+
+def test_prefill_over_an_fp8_cache_of_128_dim_heads(tb):
+    """The reference's second test geometry (32 query heads, 8 kv heads, 128 dims: tests/test_fused.py:265-276)
+    on an e4m3 cache: the tensor-core prefill kernel is built for 256-dim heads, so the chunk goes through the
+    M-row decode kernel in groups of rows; same call, same bar."""
+    from types import SimpleNamespace
+    hq, hkv, d, pos, T = 32, 8, 128, 37, 150
+    cfg = SimpleNamespace(n_heads=hq, n_kv_heads=hkv, head_dim=d, attn_layers=[0])
+    kb, vb = O.seeded_bf16(711, hkv, pos + T, d), O.seeded_bf16(712, hkv, pos + T, d)
+    qb = O.seeded_bf16(713, T, hq, d)
+    st = tb.State(cfg, pos + T + 40, "cuda", kv_dtype=F8)
+    tb.fused.kv_write_prefill(to_dev(kb[:, :pos]), to_dev(vb[:, :pos]), st, 0, 0)
+    o = _prefill(tb, cfg, st, qb, kb[:, pos:], vb[:, pos:], pos)
+    ref = oracle_state_from(st)
+    kd, vd = ref.dequant(0, pos + T)
+    want = O.attn_prefill(O.bf16_bits_to_f32(qb), kd, vd, pos)
+    assert_attn_close(f32_of(o), want, "fp8 cache, 128-dim heads")
+    assert tb._lib.device_status() == 0

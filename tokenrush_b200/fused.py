@@ -263,16 +263,16 @@ def attn_prefill_fused(q, k_cache, v_cache, pos, cfg, k_scale=None, v_scale=None
     if q.dtype != torch.bfloat16 or not q.is_contiguous():
         raise ValueError("q must be contiguous bf16 [T, HQ, D]")
     cache = _cache(k_cache, v_cache, k_scale, v_scale)
-    if k_cache.dtype == torch.bfloat16 and D != 256:
+    if D != 256:
         # The tensor-core prefill kernel is built for 256-dim heads (e4m3 or bf16 cache; the reference's
-        # default is bf16, tokenrush/fused.py:523-533 with FP8 = False).  A bf16 cache of another head
-        # size goes through the M-row decode kernel, in groups of as many rows as one launch takes.
+        # default is bf16, tokenrush/fused.py:523-533 with FP8 = False).  Caches of another head size
+        # go through the M-row decode kernel, in groups of as many rows as one launch takes.
         HKV = k_cache.shape[0]
         m_max = max(1, 48 // (HQ // HKV))
         o = torch.empty_like(q)
         for s0 in range(0, T, m_max):
             m = min(m_max, T - s0)
-            _decode(q[s0:s0 + m].reshape(m, HQ * D), k_cache, v_cache, int(pos) + s0, HQ, HKV, D, None, None, new_rows=1,
+            _decode(q[s0:s0 + m].reshape(m, HQ * D), k_cache, v_cache, int(pos) + s0, HQ, HKV, D, k_scale, v_scale, new_rows=1,
                     out=o[s0:s0 + m].view(m, HQ * D))
         return o
     o = torch.empty_like(q)
