@@ -188,3 +188,26 @@ def test_add_rmsnorm_after_the_output_projection(tb, golden_dir):
                                    st.k_scale[0], st.v_scale[0])
     assert o.shape == (2, HQ * D) and o.is_contiguous() and o.dtype == torch.bfloat16
     assert tb._lib.device_status() == 0
+
+
+def test_launch_count_counts_the_library_kernels(tb):
+    """trb_launch_count: one per kernel the library launches (append, decode, cursor update), nothing for
+    calls that fail their argument checks."""
+    lib = tb._lib.lib()
+    cfg = tb.AttnConfig(n_attn=1)
+    st = tb.State(cfg, 512, "cuda", kv_dtype=F8)
+    k = to_dev(O.seeded_bf16(91, HKV, 40, D))
+    tb.fused.kv_write_prefill(k, k, st, 0, 0)                       # the workspace of the decode below exists afterwards
+    st.set_pos(39)
+    q = to_dev(O.seeded_bf16(92, 1, HQ * D))
+    tb.fused.attn_decode_fused(q, None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0], st.v_scale[0])
+    n0 = lib.trb_launch_count()
+    tb.fused.kv_write_prefill(k[:, :1], k[:, :1], st, 0, st.pos_t)
+    tb.fused.attn_decode_fused(q, None, st.k[0], st.v[0], st.pos_t, cfg, st.k_scale[0], st.v_scale[0])
+    tb.fused.cursor_advance(st.pos_t, 1)
+    assert lib.trb_launch_count() - n0 == 3
+    with pytest.raises(Exception):
+        tb.fused.kv_append(k[:, :1].float(), k[:, :1].float(), st.k[0], st.v[0], 0, st.k_scale[0], st.v_scale[0])
+    assert lib.trb_launch_count() - n0 == 3
+    torch.cuda.synchronize()
+    assert tb._lib.device_status() == 0
