@@ -673,7 +673,7 @@ def run_profile_case(args):
         a = buf[63, :32].astype(np.int64)
         t0 = a[0, 0]
         names = ["sm pass start", "sm S ready", "sm S loaded", "sm max done", "sm barrier passed", "sm PV(i-1) done", "sm P written", "sm P published",
-                 "mma qk entry", "mma K landed", "mma S buffer free", "mma QK issued", "mma pv entry", "mma V landed", "mma P ready", "mma PV issued"]
+                 "mma qk entry", "mma K landed", "mma K landed (again)", "mma QK issued", "mma pv entry", "mma V landed", "mma P ready", "mma PV issued"]
         print("clock64 cycles relative to the first stamp; one line per key tile (softmax warp 0, then the MMA warp)")
         print(" | ".join(names))
         for r in a:
